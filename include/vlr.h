@@ -1,0 +1,210 @@
+/*
+ * libvlr - C ABI of the B200 (sm_100a) multi-LoRA batching operator.
+ *
+ * Plain pointers and sizes only.  Every pointer named "device" must be device
+ * memory of the current CUDA device; the library allocates nothing and keeps
+ * no state between calls except a cached driver entry point for tensor-map
+ * encoding.  All work is enqueued on the stream passed in (a cudaStream_t cast
+ * to void*; NULL = the legacy default stream) and the calls return without
+ * synchronising.
+ *
+ * Return value: 0 on success, a negative VLR_ERR_* code when host-side argument
+ * validation fails (nothing was launched), or a positive cudaError_t value
+ * when a launch failed.  vlr_error_string() explains either.
+ *
+ * The citations give the reference interface each entry point replaces
+ * (paths relative to the reference project root).
+ */
+#ifndef VLR_H_
+#define VLR_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VLR_OK 0
+#define VLR_ERR_NULL -1          /* a required pointer is NULL */
+#define VLR_ERR_SHAPE -2         /* unsupported feature sizes / ranks */
+#define VLR_ERR_DTYPE -3         /* dtype is neither VLR_F16 nor VLR_BF16 */
+#define VLR_ERR_ALIGN -4         /* a pointer or row pitch is not 16-byte aligned */
+#define VLR_ERR_WORKSPACE -5     /* workspace too small */
+#define VLR_ERR_RANGE -6         /* a count or capacity is out of range */
+#define VLR_ERR_DRIVER -7        /* tensor-map encoding is unavailable or failed */
+#define VLR_ERR_UNSUPPORTED -8   /* valid request this build does not implement */
+
+#define VLR_F16 0
+#define VLR_BF16 1
+
+/* Layout of the B side of an adapter slot in the pool. */
+#define VLR_LAYOUT_PUNICA 0 /* the slot's r cells hold the flat bytes of [H_out, r]
+                               (valora/csrc/bgmv/bgmv_impl.cuh:174-179) */
+#define VLR_LAYOUT_ROWS 1   /* cell k of the slot is row k of B [r, H_out]
+                               (atmm/valora/csrc/bgmv/bgmv_impl.cuh:114-123) */
+
+/* flags of vlr_atmm */
+#define VLR_ATMM_ACCUMULATE_SHRINK 1 /* shrink adds into y (reference epilogue beta = 1,
+                                        atmm/valora/csrc/bgmv/bgmv_impl.cuh:174); default overwrites */
+#define VLR_ATMM_APPLY_SCALE 2       /* expand multiplies by lora_scales[adapter]; the reference
+                                        epilogue uses alpha = 1 (same file :174, :236) */
+
+/* kinds in the tile schedule written by vlr_pack */
+#define VLR_TILE_MMA 0
+#define VLR_TILE_GATHER 1
+#define VLR_TILE_INTS 8   /* int32 per tile: kind, adapter, rank, first, nrows, segment, sorted_pos, 0 */
+
+/* indices into the counts array written by vlr_pack */
+#define VLR_COUNT_SEGMENTS 0
+#define VLR_COUNT_MMA_TILES 1
+#define VLR_COUNT_GATHER_TILES 2
+#define VLR_COUNT_GATHER_ROWS 3
+#define VLR_COUNT_STATUS 4     /* 0 ok, 1 an adapter id was out of range, 2 tile capacity exceeded */
+#define VLR_COUNT_INTS 8
+
+int vlr_version(void);
+const char* vlr_error_string(int code);
+
+/*
+ * Decode gather mat-vec.  Replaces valora._kernels.dispatch_bgmv
+ * (valora/csrc/lora_ops.cc:76-126; kernels valora/csrc/bgmv/bgmv_impl.cuh:14-241).
+ *
+ * h_in >= h_out selects the shrink: for token b with adapter a = indicies[b],
+ * r = a_len[a] / 4, and j < r:
+ *     y[b, j] = sum_k x[b, k] * w[a_loc[a_start[a] + r*qkvo + j], k]     (overwrites)
+ * h_in < h_out selects the expand (x is [batch, h_in] with h_in = the buffer's
+ * rank width; only the first r columns are read):
+ *     y[b, o] += scale[a] * sum_{k<r} x[b, k] * B_a[k, o]
+ * with B_a addressed per `layout`.  fp32 accumulation, one rounding to dtype.
+ * w is [cells, H] with H = max(h_in, h_out) elements per cell.  r must be a
+ * multiple of 8 and at most 128; H a multiple of 8.
+ * All pointers device.  lora_scales has dtype `dtype`, one entry per adapter.
+ */
+int vlr_bgmv(void* y, const void* x, const void* w,
+             const int64_t* a_start, const int64_t* a_len, const int64_t* a_loc,
+             const int64_t* indicies, int64_t qkvo, const void* lora_scales,
+             int64_t batch, int64_t h_in, int64_t h_out, int dtype, int layout, void* stream);
+
+/*
+ * Ragged grouped shrink / expand on the tensor cores.  Replaces
+ * atmm_ops.dispatch_bgmv (atmm/valora/csrc/lora_ops.cc:115-186; host driver and
+ * problem table atmm/valora/csrc/bgmv/bgmv_impl.cuh:76-125, 269-383).
+ *
+ * Problem i (i < num_problems): m = output_counts[i] rows starting at row
+ * start_ids[i], rank r = rank_counts[i], adapter lora_ids[i]; the slot's r
+ * weight rows are the r CONSECUTIVE cells from a_loc[a_start[adapter] + r*qkvo].
+ * h_in >= h_out: shrink  y[rows, :r]  = x[rows, :] * W^T      (y is [T, h_out])
+ * h_in <  h_out: expand  y[rows, :]  += x[rows, :r] * W       (x is [T, h_in])
+ * fp32 accumulation in tensor memory, one rounding to dtype.  Ranks must be
+ * multiples of 8 and at most 128.  a_len, indicies and tmp are accepted for
+ * signature parity and not read; tmp may be NULL.  w is [w_cells, H].
+ */
+int vlr_atmm(void* y, const void* x, const void* w,
+             const int64_t* a_start, const int64_t* a_len, const int64_t* a_loc,
+             const int64_t* indicies, int64_t qkvo, const void* lora_scales,
+             const int64_t* output_counts, const int64_t* rank_counts,
+             const int64_t* lora_ids, const int64_t* start_ids,
+             void* tmp, int64_t tmp_bytes, int64_t num_problems,
+             int64_t T, int64_t h_in, int64_t h_out, int64_t w_cells,
+             int dtype, int flags, void* stream);
+
+/*
+ * On-device ragged-batch packing.  Replaces the host metadata build
+ * ModelRpcServer.set_sgmm_args (valora/server/router/model_infer/model_rpc.py:265-374)
+ * and implements what count_consecutive_requests
+ * (atmm/valora/csrc/bgmv/bgmv_impl.cuh:39-72) was meant to do.
+ *
+ * tok_adapter[T] is the adapter id of every token in batch order; a_len[a] is
+ * 4 * rank(a) as in the reference's index tables.  sort != 0: perm = stable
+ * argsort(tok_adapter); sort == 0: perm = identity (reference order).  The run
+ * length encoding of tok_adapter[perm] gives the segments:
+ *   seg_len = output_counts, seg_rank = rank_counts, seg_adapter = lora_ids,
+ *   seg_start = start_ids (P+1 entries, last = T).
+ * The tile schedule (see VLR_TILE_*) cuts runs of consecutive original rows of
+ * at least mma_min_rows rows into tiles of tile_m rows and groups the other
+ * rows per adapter, gather_rows_per_tile at a time, listing their original
+ * rows in gather_rows.  counts[VLR_COUNT_INTS] receives the totals.
+ * Capacities: perm, gather_rows: T; seg_*: min(T, n_adapters or T) + 1;
+ * tiles: tiles_cap tiles of VLR_TILE_INTS int32.
+ */
+size_t vlr_pack_workspace_bytes(int64_t T, int64_t n_adapters);
+int vlr_pack(const int64_t* tok_adapter, int64_t T, const int64_t* a_len, int64_t n_adapters,
+             int sort, int tile_m, int mma_min_rows, int gather_rows_per_tile,
+             int32_t* perm, int64_t* seg_len, int64_t* seg_rank, int64_t* seg_adapter,
+             int64_t* seg_start, int32_t* tiles, int64_t tiles_cap, int32_t* gather_rows,
+             int32_t* counts, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Index-table compaction after adapters are offloaded.  Replaces
+ * var_len_copy_kernel_triton (valora/server/router/model_infer/infer_adapter.py:263-282):
+ * new_loc[new_start[i] + k] = old_loc[old_start[i] + k] for k < len[i], i < n.
+ */
+int vlr_var_len_copy(const int64_t* old_start, const int64_t* len, const int64_t* old_loc,
+                     const int64_t* new_start, int64_t* new_loc, int64_t n, void* stream);
+
+/* Bind the calling thread's CUDA runtime state to a device (cudaSetDevice). */
+int vlr_set_device(int device);
+
+/* Device-side status word: 0 ok, 1 a bounded wait inside a tensor-core kernel
+ * gave up (the kernel returned early and its output is incomplete).
+ * Synchronises the device.  reset != 0 clears it. */
+int vlr_device_status(int reset);
+
+/*
+ * One step over many projections: shrink then expand of every (layer, projection)
+ * problem of a packed batch, enqueued as four batched launches (tensor-core
+ * shrink, gather shrink, tensor-core expand, gather expand) that cover all
+ * problems at once.  No counterpart in the reference, which issues 6-8 calls per
+ * layer from Python with a host synchronisation after each
+ * (valora/models/peft/lora_unordered_batch_infer.py:946-988).
+ *
+ * A problem is y[T, h_out] += scale[a] * (x[T, h_in] A_a) B_a over the packed
+ * batch.  A rows live in pool wa ([cells_a, h_in], cell = one rank row), B rows
+ * in pool wb ([cells_b, h_out], cell = one row of B; the r cells of a slot are
+ * consecutive for tensor-core tiles).  The slot of adapter a starts at cell
+ * a_loc[a_start[a] + rank(a) * slot].
+ *
+ * vlr_step_plan_build fills plan_host (vlr_step_plan_bytes(n) bytes, host memory)
+ * from the problem list; the caller copies it to 128-byte aligned device memory
+ * and passes that to vlr_lora_step.  A plan stays valid while the buffers it
+ * names stay allocated; max_rows is the row capacity of every x / y buffer.
+ */
+typedef struct {
+  const void* x;            /* device [max_rows, h_in] */
+  void* y;                  /* device [max_rows, h_out] */
+  const void* wa;           /* device A-side pool */
+  const void* wb;           /* device B-side pool */
+  const int64_t* a_start_a; /* device index tables of the A-side pool */
+  const int64_t* a_loc_a;
+  const int64_t* a_start_b; /* device index tables of the B-side pool */
+  const int64_t* a_loc_b;
+  int64_t cells_a;
+  int64_t cells_b;
+  int32_t h_in;
+  int32_t h_out;
+  int32_t slot_a;
+  int32_t slot_b;
+} vlr_problem_t;
+
+size_t vlr_step_plan_bytes(int n_problems);
+int vlr_step_plan_build(const vlr_problem_t* problems, int n_problems, int64_t max_rows, int dtype,
+                        void* plan_host);
+/* workspace: the shrink results, n_problems * T * 128 elements */
+size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
+/*
+ * plan_dev: device copy of the plan.  tiles / gather_rows / counts: device
+ * outputs of vlr_pack for this step's batch.  max_mma_tiles / max_gather_tiles:
+ * host-side upper bounds used to size the grids (surplus CTAs exit at once);
+ * pass <= 0 for the safe bounds derived from T.  scales: dtype[n_adapters].
+ * max_h_in / max_h_out: the largest h_in / h_out over the plan's problems.
+ */
+int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
+                  const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
+                  const int32_t* counts, const void* scales, int max_h_in, int max_h_out,
+                  int dtype, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VLR_H_ */

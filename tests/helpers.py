@@ -1,0 +1,77 @@
+"""Test helpers: reference-style pools and index tables on CPU tensors."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+def build_tables(ranks, n_slots=4, shuffle=False, contiguous_slots=True, seed=0, spare=7):
+    """a_start, a_len (= 4*rank), a_loc for adapters of the given ranks, each
+    owning n_slots*rank cells.  shuffle=True permutes the cells of the whole pool
+    (paging exercised as in the reference's bench_ops.py); with
+    contiguous_slots=True the permutation moves whole adapters only, so every
+    slot stays a run of consecutive cells (what the tensor-core path needs)."""
+    rng = np.random.default_rng(seed)
+    sizes = [n_slots * int(r) for r in ranks]
+    total = sum(sizes) + spare
+    if not shuffle:
+        order = list(range(len(ranks)))
+    else:
+        order = list(rng.permutation(len(ranks)))
+    a_loc_parts = [None] * len(ranks)
+    if shuffle and not contiguous_slots:
+        cells = rng.permutation(total)[:sum(sizes)]
+        off = 0
+        for a, sz in enumerate(sizes):
+            a_loc_parts[a] = cells[off:off + sz]
+            off += sz
+    else:
+        off = spare // 2
+        for a in order:
+            a_loc_parts[a] = np.arange(off, off + sizes[a])
+            off += sizes[a]
+    a_start = np.zeros(len(ranks), np.int64)
+    a_start[1:] = np.cumsum(sizes)[:-1]
+    a_loc = np.concatenate(a_loc_parts).astype(np.int64)
+    a_len = np.asarray([4 * int(r) for r in ranks], np.int64)
+    return a_start, a_len, a_loc, total
+
+
+def fill_pool_a(A, ranks, a_start, a_loc, total, width, dtype, n_slots=None, garbage=True, seed=1):
+    """A[p][a] is [H_in, r]: cell j of slot p holds A[:, j] (lora_layer_weight.py:507-510)."""
+    n_slots = len(A) if n_slots is None else n_slots
+    g = torch.Generator().manual_seed(seed)
+    pool = (torch.randn(total, width, generator=g) * (0.5 if garbage else 0.0)).to(dtype)
+    for p in range(len(A)):
+        for a, r in enumerate(ranks):
+            r = int(r)
+            cells = a_loc[a_start[a] + r * p: a_start[a] + r * (p + 1)]
+            pool[torch.from_numpy(cells)] = A[p][a].T.contiguous().to(dtype)
+    return pool
+
+
+def fill_pool_b(B, ranks, a_start, a_loc, total, width, dtype, layout="rows", garbage=True, seed=2):
+    """B[p][a] is [r, H_out].  layout 'rows': cell k = B[k, :].  layout 'punica':
+    the slot's r cells hold the flat bytes of B.T = [H_out, r] (lora_layer_weight.py:511-516)."""
+    g = torch.Generator().manual_seed(seed)
+    pool = (torch.randn(total, width, generator=g) * (0.5 if garbage else 0.0)).to(dtype)
+    for p in range(len(B)):
+        for a, r in enumerate(ranks):
+            r = int(r)
+            cells = a_loc[a_start[a] + r * p: a_start[a] + r * (p + 1)]
+            blk = B[p][a].to(dtype)
+            if layout == "punica":
+                blk = blk.T.contiguous().reshape(r, width)
+            pool[torch.from_numpy(cells)] = blk
+    return pool
+
+
+def t64(a, device):
+    return torch.from_numpy(np.asarray(a, dtype=np.int64)).to(device)
+
+
+def rand_lora(ranks, h_in, h_out, dtype, n_slots=1, seed=0, wstd=0.02):
+    g = torch.Generator().manual_seed(seed)
+    A = [[(torch.randn(h_in, int(r), generator=g) * wstd).to(dtype) for r in ranks] for _ in range(n_slots)]
+    B = [[(torch.randn(int(r), h_out, generator=g) * wstd).to(dtype) for r in ranks] for _ in range(n_slots)]
+    return A, B

@@ -1,0 +1,381 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU oracle on the
+same seeded inputs.  Bit-exact for packing and index tables; max-abs error
+<= 1e-2 against the oracle's fp32 result for fp16 / bf16 outputs."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from valora_b200 import workloads
+from tests.helpers import build_tables, fill_pool_a, fill_pool_b, rand_lora, t64
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from valora_b200 import ops as _ops
+    from valora_b200 import _lib
+    _lib.load()
+    return _ops
+
+
+def _err(got, ref32):
+    return float((got.float().cpu() - ref32).abs().max())
+
+
+# --------------------------------------------------------------------------- BGMV
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["punica", "rows"])
+@pytest.mark.parametrize("shuffle", [False, True])
+def test_bgmv_multi_rank(ops, dtype, layout, shuffle):
+    """Shape of test/kernel/test_kernel_correctness_multi_rank.py: H=1024, two
+    adapters of rank 8 and 16, 128 tokens; here both directions and both dtypes."""
+    H, ranks, N = 1024, [8, 16], 128
+    A, B = rand_lora(ranks, H, H, dtype, n_slots=4, seed=3, wstd=0.1)
+    a_start, a_len, a_loc, total = build_tables(ranks, 4, shuffle=shuffle, contiguous_slots=False, seed=5)
+    wa = fill_pool_a(A, ranks, a_start, a_loc, total, H, dtype)
+    wb = fill_pool_b(B, ranks, a_start, a_loc, total, H, dtype, layout=layout)
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(N, H, generator=g).to(dtype)
+    idx = torch.tensor([i * len(ranks) // N for i in range(N)])
+    scales = torch.tensor([1.0, 0.5]).to(dtype)
+    for qkvo in (0, 3):
+        v0 = torch.full((N, 16), 7.0).to(dtype)
+        ref_v = oracle.bgmv_shrink_ref(v0, x, wa, a_start, a_len, a_loc, idx, qkvo)
+        v = v0.to(DEV)
+        ops.bgmv(v, x.to(DEV), wa.view(total, 32, H // 32).to(DEV), t64(a_start, DEV), t64(a_len, DEV),
+                 t64(a_loc, DEV), idx.to(DEV), qkvo, scales.to(DEV))
+        assert _err(v, ref_v) <= TOL
+        # columns >= rank keep their old value (bgmv_impl.cuh:36)
+        assert torch.all(v[:N // 2, 8:].cpu() == 7.0)
+        y0 = torch.randn(N, H, generator=g).to(dtype)
+        vin = ref_v.to(dtype)
+        ref_y = oracle.bgmv_expand_ref(y0, vin, wb, a_start, a_len, a_loc, idx, qkvo, scales, layout=layout)
+        y = y0.to(DEV)
+        ops.bgmv(y, vin.to(DEV), wb.view(total, 32, H // 32).to(DEV), t64(a_start, DEV), t64(a_len, DEV),
+                 t64(a_loc, DEV), idx.to(DEV), qkvo, scales.to(DEV),
+                 layout=ops.LAYOUT_PUNICA if layout == "punica" else ops.LAYOUT_ROWS)
+        assert _err(y, ref_y) <= TOL
+
+
+def test_bgmv_config1(ops):
+    """Decode config: 512 tokens, 64 adapters of rank 64, bf16, 4096 -> 4096."""
+    b = workloads.config1()
+    fl = workloads.make_floats(b)
+    H = 4096
+    a_start, a_len, a_loc, total = build_tables(b.ranks, 1, shuffle=True, contiguous_slots=False, seed=1)
+    wa = fill_pool_a([fl["A"][0]], b.ranks, a_start, a_loc, total, H, b.dtype, garbage=False)
+    wb = fill_pool_b([fl["B"][0]], b.ranks, a_start, a_loc, total, H, b.dtype, layout="punica", garbage=False)
+    idx = torch.from_numpy(b.tok_adapter.astype(np.int64))
+    scales = torch.from_numpy(b.scalings()).to(b.dtype)
+    x, y0 = fl["X"][0], fl["Y0"][0]
+    v = torch.zeros(b.T, 64, dtype=b.dtype, device=DEV)
+    dev = lambda t: t.to(DEV)
+    ops.bgmv(v, dev(x), dev(wa).view(total, 32, 128), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
+             dev(idx), 0, dev(scales))
+    ref_v = oracle.bgmv_shrink_ref(torch.zeros(b.T, 64, dtype=b.dtype), x, wa, a_start, a_len, a_loc, idx, 0)
+    assert _err(v, ref_v) <= TOL
+    y = dev(y0)
+    ops.bgmv(y, v, dev(wb).view(total, 32, 128), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
+             dev(idx), 0, dev(scales))
+    # end to end against the operator's fp32 truth (no 16-bit rounding of V)
+    truth = y0.float().clone()
+    for t in range(b.T):
+        a = int(idx[t])
+        truth[t] += (x[t].float() @ fl["A"][0][a].float()) @ fl["B"][0][a].float() * float(scales[a])
+    assert _err(y, truth) <= TOL
+
+
+def test_bgmv_rejects_bad_arguments(ops):
+    x = torch.zeros(4, 1024, dtype=torch.float16, device=DEV)
+    y = torch.zeros(4, 16, dtype=torch.float16, device=DEV)
+    w = torch.zeros(64, 32, 32, dtype=torch.float16, device=DEV)
+    z = torch.zeros(1, dtype=torch.int64, device=DEV)
+    idx = torch.zeros(4, dtype=torch.int64, device=DEV)
+    sc = torch.ones(1, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.bgmv(y.cpu(), x, w, z, z, z, idx, 0, sc)                      # not CUDA
+    with pytest.raises(RuntimeError):
+        ops.bgmv(y, x.t(), w, z, z, z, idx, 0, sc)                        # not contiguous
+    with pytest.raises(RuntimeError):
+        ops.bgmv(y, x, w, z, z, z, idx[:3], 0, sc)                        # size mismatch
+    with pytest.raises(RuntimeError):
+        ops.bgmv(y.float(), x.float(), w.float(), z, z, z, idx, 0, sc)    # dtype
+    with pytest.raises(RuntimeError):
+        ops.bgmv(y, x, w[:, :, :16].contiguous(), z, z, z, idx, 0, sc)    # cell width != h_in
+
+
+# --------------------------------------------------------------------------- packing
+def _pack_and_compare(ops, tok, ranks, sort, tile_m=128, mma_min=16, grp=8):
+    tok = np.asarray(tok, np.int64)
+    ranks = np.asarray(ranks, np.int64)
+    T = tok.shape[0]
+    packer = ops.Packer(max(T, 1), len(ranks), DEV, tile_m, mma_min, grp)
+    pk = packer.pack(torch.from_numpy(tok).to(DEV), torch.from_numpy(ranks * 4).to(DEV), sort=sort)
+    torch.cuda.synchronize()
+    c = pk.host_counts()
+    ref = oracle.pack_sorted_ref(tok, ranks, sort=sort)
+    P = ref["P"]
+    assert c["status"] == 0
+    assert c["P"] == P
+    assert np.array_equal(pk.perm[:T].cpu().numpy(), ref["perm"])
+    assert np.array_equal(pk.seg_len[:P].cpu().numpy(), ref["seg_len"])
+    assert np.array_equal(pk.seg_rank[:P].cpu().numpy(), ref["seg_rank"])
+    assert np.array_equal(pk.seg_adapter[:P].cpu().numpy(), ref["seg_adapter"])
+    assert np.array_equal(pk.seg_start[:P + 1].cpu().numpy(), ref["seg_start"])
+    tiles, grows, n_mma, n_g = oracle.tile_schedule_ref(tok, ranks, ref["perm"], tile_m, mma_min, grp)
+    assert (c["n_mma"], c["n_gather"], c["n_gather_rows"]) == (n_mma, n_g, len(grows))
+    assert np.array_equal(pk.tiles[:n_mma + n_g].cpu().numpy(), tiles)
+    assert np.array_equal(pk.gather_rows[:len(grows)].cpu().numpy(), grows)
+    return pk, ref
+
+
+@pytest.mark.parametrize("sort", [True, False])
+def test_pack_edge_cases(ops, sort):
+    ranks = [8, 16, 64, 128, 32]
+    _pack_and_compare(ops, [], ranks, sort)
+    _pack_and_compare(ops, [3], ranks, sort)
+    _pack_and_compare(ops, [2] * 300, ranks, sort)
+    _pack_and_compare(ops, [0, 1, 2, 3, 4] * 50, ranks, sort)
+    _pack_and_compare(ops, [4] * 15 + [1] * 16 + [4] * 17 + [0] * 129 + [1], ranks, sort)
+    _pack_and_compare(ops, [4] * 15 + [1] * 16 + [4] * 17, ranks, sort, tile_m=16, mma_min=4, grp=3)
+
+
+@pytest.mark.parametrize("cfg", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("sort", [True, False])
+def test_pack_configs(ops, cfg, sort):
+    b = workloads.CONFIGS[cfg]()
+    _pack_and_compare(ops, b.tok_adapter, b.ranks, sort)
+
+
+def test_pack_random_and_reference_offsets(ops):
+    rng = np.random.default_rng(0)
+    for T, n in ((1000, 7), (5000, 300), (257, 2), (4097, 1024)):
+        ranks = rng.choice([8, 16, 32, 64, 128], size=n)
+        # requests of random length, as the engine's repeat_interleave builds them
+        req = rng.integers(0, n, size=T // 5 + 1)
+        lens = rng.integers(1, 10, size=req.shape[0])
+        tok = np.repeat(req, lens)[:T]
+        _pack_and_compare(ops, tok, ranks, True)
+        pk, ref = _pack_and_compare(ops, tok, ranks, False)
+    # reference order reproduces the host packer's offsets: cat([0], cumsum(counts))
+    oc, _, si, npb = oracle.set_sgmm_args_ref(["a", "b", "a", "a", "c"], [300, 12, 1, 44, 128], True)
+    tok = np.repeat([0, 1, 0, 0, 2], [300, 12, 1, 44, 128])
+    pk, ref = _pack_and_compare(ops, tok, [64, 64, 64], False)
+    P = npb[0]
+    assert np.array_equal(pk.seg_len[:P].cpu().numpy(), oc[:P])
+    assert np.array_equal(pk.seg_start[:P + 1].cpu().numpy(), si[:P + 1])
+
+
+def test_pack_flags_bad_adapter_id(ops):
+    packer = ops.Packer(8, 4, DEV)
+    tok = torch.tensor([0, 1, 9, 2], dtype=torch.int64, device=DEV)
+    pk = packer.pack(tok, torch.full((4,), 64, dtype=torch.int64, device=DEV))
+    assert pk.host_counts()["status"] == 1
+
+
+# --------------------------------------------------------------------------- ATMM (tensor cores)
+def _atmm_case(ops, dtype, ranks, seg_len, seg_ad, h, qkvo=0, n_slots=1, seed=0, shuffle=True):
+    A, B = rand_lora(ranks, h, h, dtype, n_slots=n_slots, seed=seed)
+    a_start, a_len, a_loc, total = build_tables(ranks, n_slots, shuffle=shuffle, contiguous_slots=True, seed=seed)
+    wa = fill_pool_a(A, ranks, a_start, a_loc, total, h, dtype)
+    wb = fill_pool_b(B, ranks, a_start, a_loc, total, h, dtype, layout="rows")
+    T = int(sum(seg_len))
+    g = torch.Generator().manual_seed(seed + 100)
+    x = torch.randn(T, h, generator=g).to(dtype)
+    y0 = torch.randn(T, h, generator=g).to(dtype)
+    P = len(seg_len)
+    oc = np.asarray(seg_len, np.int64)
+    rc = np.asarray([ranks[a] for a in seg_ad], np.int64)
+    li = np.asarray(seg_ad, np.int64)
+    si = np.concatenate([[0], np.cumsum(oc)]).astype(np.int64)
+    R = max(int(r) for r in ranks)
+    R = max(R, 16)
+    poison = 123.0
+    v0 = torch.full((T, R), poison).to(dtype)
+    ref_v = oracle.atmm_shrink_ref(v0, x, wa, a_start, a_loc, qkvo, oc, rc, li, si, P)
+    idx = torch.zeros(T, dtype=torch.int64)
+    scales = torch.tensor([16.0 / r for r in ranks]).to(dtype)
+    dev = lambda t: t.to(DEV)
+    args_tail = (t64(oc, DEV), t64(rc, DEV), t64(li, DEV), t64(si, DEV), None, P)
+    v = dev(v0)
+    ops.atmm(v, dev(x), dev(wa).view(total, 1, h), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
+             dev(idx), qkvo, dev(scales), *args_tail)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert _err(v, ref_v) <= TOL
+    # columns >= rank of each segment are untouched
+    vc = v.cpu().float()
+    for s in range(P):
+        assert torch.all(vc[si[s]:si[s + 1], rc[s]:] == poison)
+    vin = ref_v.to(dtype)
+    ref_y = oracle.atmm_expand_ref(y0, vin, wb, a_start, a_loc, qkvo, oc, rc, li, si, P, scales=scales)
+    y = dev(y0)
+    ops.atmm(y, dev(vin), dev(wb).view(total, 1, h), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
+             dev(idx), qkvo, dev(scales), *args_tail, apply_scale=True)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert _err(y, ref_y) <= TOL
+    return x, y0, A, B, scales
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_atmm_small(ops, dtype):
+    _atmm_case(ops, dtype, [16, 32], [40, 130], [0, 1], 256)
+
+
+@pytest.mark.parametrize("rank", [8, 16, 32, 64, 128])
+def test_atmm_ragged_lengths(ops, rank):
+    """every rank x segment lengths around the 32-row box and 128-row tile edges"""
+    lens = [1, 2, 31, 32, 33, 63, 64, 65, 127, 128, 129, 513]
+    _atmm_case(ops, torch.bfloat16, [rank, rank], lens, [i % 2 for i in range(len(lens))], 512, seed=rank)
+
+
+def test_atmm_slots_and_mixed_ranks(ops):
+    ranks = [8, 16, 24, 64, 128, 40]
+    lens = [37, 256, 1, 1, 120, 513, 5, 77]
+    ads = [0, 1, 2, 3, 1, 0, 4, 5]
+    for qkvo in (0, 2, 3):
+        _atmm_case(ops, torch.float16, ranks, lens, ads, 1024, qkvo=qkvo, n_slots=4, seed=qkvo)
+
+
+def test_atmm_config0(ops):
+    """Benchmark config 0 whole: fp16, 4096 -> 4096, ranks {8,16,16,32}, six segments."""
+    b = workloads.config0()
+    x, y0, A, B, scales = _atmm_case(ops, b.dtype, [int(r) for r in b.ranks], b.req_len.tolist(),
+                                     b.req_adapter.tolist(), 4096, seed=0)
+
+
+def test_atmm_legacy_accumulate_and_empty(ops):
+    dtype, h, ranks = torch.float16, 256, [16]
+    A, B = rand_lora(ranks, h, h, dtype, seed=9)
+    a_start, a_len, a_loc, total = build_tables(ranks, 1)
+    wa = fill_pool_a(A, ranks, a_start, a_loc, total, h, dtype)
+    x = torch.randn(50, h).to(dtype)
+    v0 = torch.randn(50, 16).to(dtype)
+    oc, rc, li, si = [50], [16], [0], [0, 50]
+    ref = oracle.atmm_shrink_ref(v0, x, wa, a_start, a_loc, 0, oc, rc, li, si, 1, accumulate=True)
+    v = v0.to(DEV)
+    idx = torch.zeros(50, dtype=torch.int64, device=DEV)
+    ops.atmm(v, x.to(DEV), wa.view(total, 1, h).to(DEV), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
+             idx, 0, None, t64(oc, DEV), t64(rc, DEV), t64(li, DEV), t64(si, DEV), None, 1,
+             accumulate_shrink=True)
+    assert _err(v, ref) <= TOL
+    # zero problems: nothing launched, output untouched
+    v2 = v0.to(DEV)
+    ops.atmm(v2, x.to(DEV), wa.view(total, 1, h).to(DEV), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
+             idx, 0, None, t64(oc, DEV), t64(rc, DEV), t64(li, DEV), t64(si, DEV), None, 0)
+    assert torch.equal(v2.cpu(), v0)
+
+
+# --------------------------------------------------------------------------- pool + compaction
+def test_var_len_copy_and_pool(ops):
+    from valora_b200.pool import AdapterPool
+    pool = AdapterPool(cells=512, width=256, n_slots=4, dtype=torch.float16, device=DEV)
+    ranks = {"a": 8, "b": 16, "c": 32, "d": 8}
+    blocks = {}
+    for name, r in ranks.items():
+        blocks[name] = [torch.randn(r, 256).half() for _ in range(4)]
+        pool.load_adapter(name, r, 16.0 / r, [blocks[name]])
+    old = (pool.a_start.cpu().numpy(), pool.a_len.cpu().numpy(), pool.a_loc.cpu().numpy())
+    pool.offload_adapters(["a", "c"])
+    keep = [0, 2]
+    n_cells = old[1][keep]                      # 4 * rank = cells with 4 slots
+    new_start = np.concatenate([[0], np.cumsum(n_cells)[:-1]])
+    ref = oracle.var_len_copy_ref(old[0][keep], n_cells, old[2], new_start, n_cells.sum())
+    assert np.array_equal(pool.a_loc.cpu().numpy(), ref)
+    assert pool.names == ["a", "c"]
+    assert pool.can_use_mem_size == 512 - 4 * (8 + 32)
+    # contents still addressable through the compacted tables
+    for i, name in enumerate(pool.names):
+        r = ranks[name]
+        loc = pool.a_loc[pool.a_start[i]: pool.a_start[i] + 4 * r]
+        for p in range(4):
+            assert torch.equal(pool.buffer[0][loc[p * r:(p + 1) * r]].cpu(), blocks[name][p])
+
+
+def test_dropin_modules(ops):
+    from valora_b200 import dropin
+    dropin.install(force=True)
+    from atmm_ops import dispatch_bgmv as dispatch_sgmm
+    from valora._kernels import dispatch_bgmv
+    H, ranks, N = 512, [16], 8
+    A, B = rand_lora(ranks, H, H, torch.float16, n_slots=4, seed=1, wstd=0.1)
+    a_start, a_len, a_loc, total = build_tables(ranks, 4)
+    wa = fill_pool_a(A, ranks, a_start, a_loc, total, H, torch.float16)
+    x = torch.randn(N, H).half()
+    idx = torch.zeros(N, dtype=torch.int64)
+    sc = torch.ones(1).half()
+    ref = oracle.bgmv_shrink_ref(torch.zeros(N, 16).half(), x, wa, a_start, a_len, a_loc, idx, 1)
+    v = torch.zeros(N, 16, dtype=torch.float16, device=DEV)
+    dispatch_bgmv(v, x.to(DEV), wa.view(total, 8, 64).to(DEV), t64(a_start, DEV), t64(a_len, DEV),
+                  t64(a_loc, DEV), idx.to(DEV), 1, sc.to(DEV))
+    assert _err(v, ref) <= TOL
+    v2 = torch.zeros(N, 16, dtype=torch.float16, device=DEV)
+    dispatch_sgmm(v2, x.to(DEV), wa.view(total, 8, 64).to(DEV), t64(a_start, DEV), t64(a_len, DEV),
+                  t64(a_loc, DEV), idx.to(DEV), 1, sc.to(DEV), t64([N], DEV), t64([16], DEV), t64([0], DEV),
+                  t64([0, N], DEV), torch.zeros(60, dtype=torch.int8, device=DEV), 1, 64, 32, 32, 32, 32, 32)
+    assert _err(v2, ref) <= TOL
+
+
+# --------------------------------------------------------------------------- step (packed batch, many problems)
+def _step_case(ops, batch, proj_ids, layers=1, mma_min=16):
+    from valora_b200.engine import LoraStepEngine
+    projs = [batch.projections[p] for p in proj_ids]
+    eng = LoraStepEngine(projs, batch.ranks, batch.scalings(), batch.dtype, DEV, layers, batch.T,
+                         mma_min_rows=mma_min)
+    g = torch.Generator().manual_seed(batch.seed)
+    W = {}
+    for layer in range(layers):
+        for p, (_, hi, ho) in enumerate(projs):
+            for a in range(batch.n_adapters):
+                r = int(batch.ranks[a])
+                A = (torch.randn(hi, r, generator=g) * 0.02).to(batch.dtype)
+                B = (torch.randn(r, ho, generator=g) * 0.02).to(batch.dtype)
+                W[(layer, p, a)] = (A, B)
+                eng.set_adapter_weights(layer, p, a, A, B)
+    X, Y0 = {}, {}
+    for layer in range(layers):
+        for p, (_, hi, ho) in enumerate(projs):
+            X[(layer, p)] = torch.randn(batch.T, hi, generator=g).to(batch.dtype)
+            Y0[(layer, p)] = torch.randn(batch.T, ho, generator=g).to(batch.dtype)
+            eng.x[layer][p].copy_(X[(layer, p)])
+            eng.y[layer][p].copy_(Y0[(layer, p)])
+    tok = torch.from_numpy(batch.tok_adapter.astype(np.int64)).to(DEV)
+    eng.step(tok)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    sc = batch.scalings()
+    for layer in range(layers):
+        for p in range(len(projs)):
+            truth = Y0[(layer, p)].float().clone()
+            xf = X[(layer, p)].float()
+            for a in np.unique(batch.tok_adapter):
+                rows = torch.from_numpy(np.nonzero(batch.tok_adapter == a)[0])
+                A, B = W[(layer, p, int(a))]
+                truth[rows] += (xf[rows] @ A.float()) @ B.float() * float(sc[a])
+            assert _err(eng.y[layer][p], truth) <= TOL, (layer, p)
+    return eng
+
+
+def test_step_config0(ops):
+    _step_case(ops, workloads.config0(), [0])
+
+
+def test_step_config3_mixed_two_widths(ops):
+    """mixed prefill + decode batch of config 3, one layer, q / up / down projections
+    (4096->4096, 4096->11008, 11008->4096): tensor-core tiles and gather tiles together"""
+    _step_case(ops, workloads.config3(layers=1), [0, 4, 6])
+
+
+def test_step_config2_hetero_ranks_two_layers(ops):
+    b = workloads.config2()
+    _step_case(ops, b, [0, 3], layers=2)
+
+
+def test_step_all_gather_rows(ops):
+    """decode-only batch (config 1): every row goes through the gather path"""
+    _step_case(ops, workloads.config1(), [0])

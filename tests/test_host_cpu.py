@@ -1,0 +1,102 @@
+"""CPU-only checks: the C-ABI library loads and exports what the header
+declares, host-side validation returns the documented codes, workload
+generators and the schedule oracle are self-consistent."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from valora_b200 import _lib, workloads
+from valora_b200.pool import AdapterPool
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _lib.declared_symbols()
+    assert {"vlr_bgmv", "vlr_atmm", "vlr_pack", "vlr_lora_step", "vlr_var_len_copy"} <= set(names)
+    for n in names:
+        assert hasattr(lib, n), n
+    assert lib.vlr_version() >= 1
+
+
+def test_host_validation_codes_without_a_gpu():
+    lib = _lib.load()
+    null = ctypes.c_void_p(0)
+    one = ctypes.c_void_p(16)
+    # nothing is launched: validation fails first
+    assert lib.vlr_bgmv(null, null, null, null, null, null, null, 0, null, 4, 4096, 64, 0, 0, null) == -1
+    assert lib.vlr_bgmv(one, one, one, one, one, one, one, 0, one, 4, 4096, 64, 7, 0, null) == -3
+    assert lib.vlr_bgmv(one, one, one, one, one, one, one, 0, one, 4, 4096, 256, 0, 0, null) == -2
+    assert lib.vlr_bgmv(one, one, one, one, one, one, one, 0, one, 0, 4096, 64, 0, 0, null) == 0   # empty batch
+    assert lib.vlr_atmm(one, one, one, one, one, one, one, 0, one, one, one, one, one, null, 0, 3,
+                        100, 4096, 60, 10, 0, 0, null) == -2                                    # rank width % 8
+    assert lib.vlr_atmm(one, one, one, one, one, one, one, 0, one, one, one, one, one, null, 0, 0,
+                        100, 4096, 64, 10, 0, 0, null) == 0                                     # no problems
+    assert lib.vlr_pack_workspace_bytes(1000, 64) > 0
+    assert lib.vlr_pack(one, 10, one, 20000, 1, 128, 16, 8, one, one, one, one, one, one, 10, one, one,
+                        one, 1 << 20, null) == -6                                               # too many adapters
+    assert lib.vlr_pack(one, 10, one, 8, 1, 128, 16, 8, one, one, one, one, one, one, 10, one, one,
+                        one, 16, null) == -5                                                    # workspace too small
+    assert lib.vlr_step_plan_bytes(3) == 3 * lib.vlr_step_plan_bytes(1) > 0
+    assert lib.vlr_lora_step(null, 2, 10, null, null, 0, 0, null, null, 4096, 4096, 0, null, 0, null) == -1
+    assert b"workspace" in lib.vlr_error_string(-5)
+
+
+def test_ops_refuse_cpu_tensors():
+    from valora_b200 import ops
+    x = torch.zeros(4, 64, dtype=torch.float16)
+    z = torch.zeros(1, dtype=torch.int64)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ops.bgmv(torch.zeros(4, 16, dtype=torch.float16), x, torch.zeros(8, 1, 64, dtype=torch.float16),
+                 z, z, z, torch.zeros(4, dtype=torch.int64), 0, torch.ones(1, dtype=torch.float16))
+
+
+def test_workloads_are_deterministic_and_shaped():
+    for i in range(5):
+        a, b = workloads.CONFIGS[i](), workloads.CONFIGS[i]()
+        assert np.array_equal(a.tok_adapter, b.tok_adapter) and np.array_equal(a.ranks, b.ranks)
+    c0 = workloads.config0()
+    assert c0.T == 928 and c0.algorithmic_flops() == 171_442_176 and c0.algorithmic_bytes() == 23_986_176
+    c1 = workloads.config1()
+    assert c1.T == 512 and c1.algorithmic_flops() == 536_870_912
+    c3 = workloads.config3()
+    assert c3.n_prefill_req == 8 and (c3.req_len[8:] == 1).all() and len(c3.req_len) == 392
+    c4 = workloads.config4()
+    assert c4.T == 16384 and int((c4.req_len > 1).sum()) == c4.n_prefill_req
+    # adapter-group sharding covers the whole box batch exactly once
+    parts = [workloads.config4(n_gpus=4, rank=r) for r in range(4)]
+    assert sum(p.T for p in parts) == c4.T
+    for r, p in enumerate(parts):
+        assert np.all(p.tok_adapter % 4 == r)
+
+
+@pytest.mark.parametrize("cfg", [0, 1, 2, 3, 4])
+def test_schedule_covers_every_token_once(cfg):
+    b = workloads.CONFIGS[cfg]()
+    pk = oracle.pack_sorted_ref(b.tok_adapter, b.ranks)
+    tiles, grows, n_mma, n_g = oracle.tile_schedule_ref(b.tok_adapter, b.ranks, pk["perm"])
+    seen = np.zeros(b.T, np.int32)
+    for t in tiles:
+        kind, a, r, first, n = t[:5]
+        rows = np.arange(first, first + n) if kind == 0 else grows[first:first + n]
+        assert np.all(b.tok_adapter[rows] == a) and r == b.ranks[a]
+        seen[rows] += 1
+    assert np.all(seen == 1)
+    assert int(pk["seg_len"].sum()) == b.T and np.all(np.diff(pk["seg_adapter"]) > 0)
+
+
+def test_pool_allocator_matches_reference_semantics():
+    pool = AdapterPool(cells=64, width=8, n_slots=4, dtype=torch.float16, device="cpu")
+    state = np.ones(64, np.uint8)
+    a = pool.alloc(10); ra = oracle.alloc_ref(state, 10)
+    b = pool.alloc(7); rb = oracle.alloc_ref(state, 7)
+    pool.free(a[2:6]); state[ra[2:6]] = 1
+    c = pool.alloc(9); rc = oracle.alloc_ref(state, 9)
+    assert np.array_equal(a, ra) and np.array_equal(b, rb) and np.array_equal(c, rc)
+    assert np.array_equal(pool.mem_state, state)
+    run = pool.alloc_contiguous(12)
+    assert np.array_equal(run, np.arange(run[0], run[0] + 12)) and np.all(state[run] == 1)
+    with pytest.raises(Exception):
+        pool.alloc(1000)

@@ -1,0 +1,367 @@
+// On-device ragged-batch packing: stable sort of tokens by adapter, run-length
+// segments, exclusive-scan offsets and the tile schedule.  Integer work only;
+// every output is a pure function of the inputs (no atomics decide an order).
+//
+// Four small launches on one stream:
+//   1. pack_hist     per-block adapter histograms (blocks of kPackBlock tokens)
+//   2. pack_scan     per-adapter exclusive prefix over blocks + adapter bases
+//   3. pack_scatter  stable placement: perm and the sorted key array
+//   4. pack_tiles    segments, chunks and the tile schedule (one CTA)
+// In reference order (sort = 0) only the last one runs.
+#include "common.cuh"
+
+namespace vlr {
+
+constexpr int kPackBlock = 256;      // tokens per histogram block
+constexpr int kPackMaxAdapters = 8192;
+constexpr int kScanThreads = 1024;
+
+struct PackWs {
+  int32_t* hist;        // [nblk][n_adapters]
+  int32_t* abase;       // [n_adapters]
+  int32_t* key;         // [T] sorted keys
+  int32_t* chunk_start; // [T+1]
+  int32_t* chunk_seg;   // [T]
+  int32_t* chunk_tile;  // [T+1] exclusive tile prefix per chunk
+  int32_t* chunk_short; // [T+1] exclusive short-row prefix per chunk
+  int32_t* seg_chunk;   // [T+1] first chunk of each segment
+  int32_t* seg_gtile;   // [T+1] exclusive gather-tile prefix per segment
+  int32_t* gpos;        // [T] sorted position of each gather row
+};
+
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static size_t pack_ws_layout(int64_t T, int64_t n_adapters, PackWs* ws, char* base) {
+  const int64_t nblk = (T + kPackBlock - 1) / kPackBlock;
+  size_t off = 0;
+  auto take = [&](int64_t n) {
+    int32_t* p = reinterpret_cast<int32_t*>(base + off);
+    off = align_up(off + (size_t)n * sizeof(int32_t), 256);
+    return p;
+  };
+  int32_t* hist = take(nblk * n_adapters);
+  int32_t* abase = take(n_adapters);
+  int32_t* key = take(T);
+  int32_t* cs = take(T + 1);
+  int32_t* cg = take(T);
+  int32_t* ct = take(T + 1);
+  int32_t* csh = take(T + 1);
+  int32_t* sc = take(T + 1);
+  int32_t* sg = take(T + 1);
+  int32_t* gp = take(T);
+  if (ws) *ws = PackWs{hist, abase, key, cs, cg, ct, csh, sc, sg, gp};
+  return off;
+}
+
+__device__ __forceinline__ int clamp_id(int64_t id, int n_adapters, int32_t* counts) {
+  if (id < 0 || id >= n_adapters) {
+    counts[VLR_COUNT_STATUS] = 1;
+    return 0;
+  }
+  return (int)id;
+}
+
+__global__ void __launch_bounds__(kPackBlock)
+pack_hist_kernel(const int64_t* __restrict__ tok, int T, int n_adapters, int32_t* hist,
+                 int32_t* counts) {
+  extern __shared__ int32_t sh[];
+  for (int a = threadIdx.x; a < n_adapters; a += kPackBlock) sh[a] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kPackBlock + threadIdx.x;
+  if (i < T) atomicAdd(&sh[clamp_id(tok[i], n_adapters, counts)], 1);
+  __syncthreads();
+  int32_t* row = hist + (int64_t)blockIdx.x * n_adapters;
+  for (int a = threadIdx.x; a < n_adapters; a += kPackBlock) row[a] = sh[a];
+}
+
+// Exclusive scan of one int per thread across a 1024-thread block.
+__device__ __forceinline__ int block_exscan(int v, int* total, int* warp_sums /*[33]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  __syncthreads();                       // protect warp_sums from a previous call
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < (int)(blockDim.x >> 5) ? warp_sums[lane] : 0;
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int n = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += n;
+    }
+    warp_sums[lane] = winc - w;
+    if (lane == 31) warp_sums[32] = winc;
+  }
+  __syncthreads();
+  *total = warp_sums[32];
+  return warp_sums[warp] + inc - v;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+pack_scan_kernel(int nblk, int n_adapters, int32_t* hist, int32_t* abase) {
+  __shared__ int warp_sums[33];
+  // per-adapter exclusive prefix over blocks; the adapter's total lands in abase
+  for (int a = threadIdx.x; a < n_adapters; a += kScanThreads) {
+    int run = 0;
+    for (int b = 0; b < nblk; ++b) {
+      int32_t* p = hist + (int64_t)b * n_adapters + a;
+      const int c = *p;
+      *p = run;
+      run += c;
+    }
+    abase[a] = run;
+  }
+  __syncthreads();
+  // exclusive scan of the totals over adapters
+  const int per = (n_adapters + kScanThreads - 1) / kScanThreads;
+  const int lo = min(threadIdx.x * per, n_adapters), hi = min(lo + per, n_adapters);
+  int sum = 0;
+  for (int a = lo; a < hi; ++a) sum += abase[a];
+  int total;
+  int run = block_exscan(sum, &total, warp_sums);
+  for (int a = lo; a < hi; ++a) {
+    const int c = abase[a];
+    abase[a] = run;
+    run += c;
+  }
+}
+
+__global__ void __launch_bounds__(kPackBlock)
+pack_scatter_kernel(const int64_t* __restrict__ tok, int T, int n_adapters,
+                    const int32_t* __restrict__ hist, const int32_t* __restrict__ abase,
+                    int32_t* perm, int32_t* key, int32_t* counts) {
+  __shared__ int keys[kPackBlock];
+  const int i = blockIdx.x * kPackBlock + threadIdx.x;
+  const int k = i < T ? clamp_id(tok[i], n_adapters, counts) : -1;
+  keys[threadIdx.x] = k;
+  __syncthreads();
+  if (i >= T) return;
+  int rank = 0;
+  for (int j = 0; j < (int)threadIdx.x; ++j) rank += keys[j] == k;
+  const int pos = abase[k] + hist[(int64_t)blockIdx.x * n_adapters + k] + rank;
+  perm[pos] = i;
+  key[pos] = k;
+}
+
+struct PackOut {
+  int32_t* perm;
+  int64_t* seg_len;
+  int64_t* seg_rank;
+  int64_t* seg_adapter;
+  int64_t* seg_start;
+  int32_t* tiles;
+  int64_t tiles_cap;
+  int32_t* gather_rows;
+  int32_t* counts;
+};
+
+// One CTA.  Thread t owns the contiguous index range [t*per, (t+1)*per) of
+// whatever is being scanned (sorted positions, chunks, segments).
+__global__ void __launch_bounds__(kScanThreads)
+pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a_len, int T,
+                  int n_adapters, int sorted, int tile_m, int mma_min, int grp, PackWs ws,
+                  PackOut out) {
+  __shared__ int warp_sums[33];
+  __shared__ int s_P, s_C;
+  const int tid = threadIdx.x;
+
+  if (!sorted) {
+    for (int i = tid; i < T; i += kScanThreads) {
+      out.perm[i] = i;
+      ws.key[i] = clamp_id(tok[i], n_adapters, out.counts);
+    }
+    __syncthreads();
+  }
+  const int32_t* key = ws.key;
+  const int32_t* row = out.perm;
+
+  // ---- pass 1: segment and chunk boundaries over sorted positions
+  {
+    const int per = (T + kScanThreads - 1) / kScanThreads;
+    const int lo = min(tid * per, T), hi = min(lo + per, T);
+    int nseg = 0, nchunk = 0;
+    for (int i = lo; i < hi; ++i) {
+      const bool sflag = i == 0 || key[i] != key[i - 1];
+      const bool cflag = sflag || row[i] != row[i - 1] + 1;
+      nseg += sflag;
+      nchunk += cflag;
+    }
+    int P, C;
+    int sbase = block_exscan(nseg, &P, warp_sums);
+    int cbase = block_exscan(nchunk, &C, warp_sums);
+    if (tid == 0) { s_P = P; s_C = C; }
+    for (int i = lo; i < hi; ++i) {
+      const bool sflag = i == 0 || key[i] != key[i - 1];
+      const bool cflag = sflag || row[i] != row[i - 1] + 1;
+      if (sflag) {
+        const int a = key[i];
+        out.seg_start[sbase] = i;
+        out.seg_adapter[sbase] = a;
+        out.seg_rank[sbase] = a_len[a] / 4;
+        ws.seg_chunk[sbase] = cbase;
+        ++sbase;
+      }
+      if (cflag) {
+        ws.chunk_start[cbase] = i;
+        ws.chunk_seg[cbase] = sbase - 1;
+        ++cbase;
+      }
+    }
+  }
+  __syncthreads();
+  const int P = s_P, C = s_C;
+  if (tid == 0) {
+    out.seg_start[P] = T;
+    ws.chunk_start[C] = T;
+    ws.seg_chunk[P] = C;
+  }
+  __syncthreads();
+  for (int s = tid; s < P; s += kScanThreads) out.seg_len[s] = out.seg_start[s + 1] - out.seg_start[s];
+
+  // ---- pass 2: per chunk, tensor-core tiles and short (gather) rows
+  int n_mma, n_short;
+  {
+    const int per = (C + kScanThreads - 1) / kScanThreads;
+    const int lo = min(tid * per, C), hi = min(lo + per, C);
+    int nt = 0, ns = 0;
+    for (int c = lo; c < hi; ++c) {
+      const int len = ws.chunk_start[c + 1] - ws.chunk_start[c];
+      if (len >= mma_min) nt += (len + tile_m - 1) / tile_m; else ns += len;
+    }
+    int tbase = block_exscan(nt, &n_mma, warp_sums);
+    int shbase = block_exscan(ns, &n_short, warp_sums);
+    for (int c = lo; c < hi; ++c) {
+      const int start = ws.chunk_start[c];
+      const int len = ws.chunk_start[c + 1] - start;
+      ws.chunk_tile[c] = tbase;
+      ws.chunk_short[c] = shbase;
+      const int seg = ws.chunk_seg[c];
+      const int a = key[start];
+      if (len >= mma_min) {
+        const int rank = (int)(a_len[a] / 4);
+        for (int m0 = 0; m0 < len; m0 += tile_m, ++tbase) {
+          if (tbase < out.tiles_cap) {
+            int32_t* t = out.tiles + (int64_t)tbase * VLR_TILE_INTS;
+            t[0] = VLR_TILE_MMA; t[1] = a; t[2] = rank; t[3] = row[start + m0];
+            t[4] = min(tile_m, len - m0); t[5] = seg; t[6] = start + m0; t[7] = 0;
+          }
+        }
+      } else {
+        for (int k = 0; k < len; ++k, ++shbase) {
+          out.gather_rows[shbase] = row[start + k];
+          ws.gpos[shbase] = start + k;
+        }
+      }
+    }
+    if (tid == 0) { ws.chunk_tile[C] = n_mma; ws.chunk_short[C] = n_short; }
+  }
+  __syncthreads();
+
+  // ---- pass 3: per segment, gather tiles over its (contiguous) short rows
+  int n_gather;
+  {
+    const int per = (P + kScanThreads - 1) / kScanThreads;
+    const int lo = min(tid * per, P), hi = min(lo + per, P);
+    int ng = 0;
+    for (int s = lo; s < hi; ++s) {
+      const int cnt = ws.chunk_short[ws.seg_chunk[s + 1]] - ws.chunk_short[ws.seg_chunk[s]];
+      ng += (cnt + grp - 1) / grp;
+    }
+    int gbase = block_exscan(ng, &n_gather, warp_sums);
+    for (int s = lo; s < hi; ++s) {
+      const int first = ws.chunk_short[ws.seg_chunk[s]];
+      const int cnt = ws.chunk_short[ws.seg_chunk[s + 1]] - first;
+      ws.seg_gtile[s] = gbase;
+      const int a = (int)out.seg_adapter[s];
+      const int rank = (int)out.seg_rank[s];
+      for (int g0 = 0; g0 < cnt; g0 += grp, ++gbase) {
+        const int64_t ti = (int64_t)n_mma + gbase;
+        if (ti < out.tiles_cap) {
+          int32_t* t = out.tiles + ti * VLR_TILE_INTS;
+          t[0] = VLR_TILE_GATHER; t[1] = a; t[2] = rank; t[3] = first + g0;
+          t[4] = min(grp, cnt - g0); t[5] = s; t[6] = ws.gpos[first + g0]; t[7] = 0;
+        }
+      }
+    }
+  }
+  if (tid == 0) {
+    out.counts[VLR_COUNT_SEGMENTS] = P;
+    out.counts[VLR_COUNT_MMA_TILES] = n_mma;
+    out.counts[VLR_COUNT_GATHER_TILES] = n_gather;
+    out.counts[VLR_COUNT_GATHER_ROWS] = n_short;
+    if ((int64_t)n_mma + n_gather > out.tiles_cap) out.counts[VLR_COUNT_STATUS] = 2;
+  }
+}
+
+__global__ void pack_clear_counts(int32_t* counts) {
+  if (threadIdx.x < VLR_COUNT_INTS) counts[threadIdx.x] = 0;
+}
+
+__global__ void var_len_copy_kernel(const int64_t* __restrict__ old_start,
+                                    const int64_t* __restrict__ len,
+                                    const int64_t* __restrict__ old_loc,
+                                    const int64_t* __restrict__ new_start,
+                                    int64_t* __restrict__ new_loc) {
+  const int64_t i = blockIdx.x;
+  const int64_t n = len[i], s = old_start[i], d = new_start[i];
+  for (int64_t k = threadIdx.x; k < n; k += blockDim.x) new_loc[d + k] = old_loc[s + k];
+}
+
+}  // namespace vlr
+
+extern "C" size_t vlr_pack_workspace_bytes(int64_t T, int64_t n_adapters) {
+  if (T < 0 || n_adapters < 0) return 0;
+  return vlr::pack_ws_layout(T, n_adapters, nullptr, nullptr) + 256;
+}
+
+extern "C" int vlr_pack(const int64_t* tok_adapter, int64_t T, const int64_t* a_len,
+                        int64_t n_adapters, int sort, int tile_m, int mma_min_rows,
+                        int gather_rows_per_tile, int32_t* perm, int64_t* seg_len,
+                        int64_t* seg_rank, int64_t* seg_adapter, int64_t* seg_start,
+                        int32_t* tiles, int64_t tiles_cap, int32_t* gather_rows, int32_t* counts,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace vlr;
+  if (!a_len || !perm || !seg_len || !seg_rank || !seg_adapter || !seg_start || !tiles ||
+      !gather_rows || !counts || !workspace)
+    return VLR_ERR_NULL;
+  if (T > 0 && !tok_adapter) return VLR_ERR_NULL;
+  if (T < 0 || T > (1 << 24) || n_adapters <= 0 || n_adapters > kPackMaxAdapters || tiles_cap < 0)
+    return VLR_ERR_RANGE;
+  if (tile_m <= 0 || mma_min_rows <= 0 || gather_rows_per_tile <= 0) return VLR_ERR_RANGE;
+  char* base = reinterpret_cast<char*>(align_up(reinterpret_cast<uintptr_t>(workspace), 256));
+  const size_t slack = base - reinterpret_cast<char*>(workspace);
+  PackWs ws;
+  const size_t need = pack_ws_layout(T, n_adapters, &ws, base);
+  if (need + slack > workspace_bytes) return VLR_ERR_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int nblk = (int)((T + kPackBlock - 1) / kPackBlock);
+  pack_clear_counts<<<1, 32, 0, s>>>(counts);
+  if (sort && T > 0) {
+    pack_hist_kernel<<<nblk, kPackBlock, n_adapters * sizeof(int32_t), s>>>(
+        tok_adapter, (int)T, (int)n_adapters, ws.hist, counts);
+    pack_scan_kernel<<<1, kScanThreads, 0, s>>>(nblk, (int)n_adapters, ws.hist, ws.abase);
+    pack_scatter_kernel<<<nblk, kPackBlock, 0, s>>>(tok_adapter, (int)T, (int)n_adapters, ws.hist,
+                                                    ws.abase, perm, ws.key, counts);
+  }
+  PackOut out{perm, seg_len, seg_rank, seg_adapter, seg_start, tiles, tiles_cap, gather_rows, counts};
+  pack_tiles_kernel<<<1, kScanThreads, 0, s>>>(tok_adapter, a_len, (int)T, (int)n_adapters,
+                                               sort && T > 0, tile_m, mma_min_rows,
+                                               gather_rows_per_tile, ws, out);
+  return launch_status();
+}
+
+extern "C" int vlr_var_len_copy(const int64_t* old_start, const int64_t* len,
+                                const int64_t* old_loc, const int64_t* new_start,
+                                int64_t* new_loc, int64_t n, void* stream) {
+  if (n == 0) return VLR_OK;
+  if (!old_start || !len || !old_loc || !new_start || !new_loc) return VLR_ERR_NULL;
+  if (n < 0 || n > 0x7fffffff) return VLR_ERR_RANGE;
+  vlr::var_len_copy_kernel<<<(unsigned)n, 256, 0, (cudaStream_t)stream>>>(old_start, len, old_loc,
+                                                                         new_start, new_loc);
+  return vlr::launch_status();
+}

@@ -1,0 +1,87 @@
+// One LoRA projection ("problem") of a step, as the batched kernels see it.
+// A step plan is an array of these in device memory, built on the host once
+// per set of buffers and reused every step.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vlr {
+
+struct alignas(128) StepProblem {
+  CUtensorMap map_x;    // [max_rows, h_in]   box 32 rows x 64 columns
+  CUtensorMap map_wa;   // [cells_a, h_in]    box 16 rows x 64 columns
+  CUtensorMap map_y;    // [max_rows, h_out]  box 32 rows x 64 columns
+  CUtensorMap map_wb;   // [cells_b, h_out]   box 16 rows x 64 columns
+  const void* x;
+  void* y;
+  const void* wa;       // A-side pool: cell = one rank row of length h_in
+  const void* wb;       // B-side pool: cell = one row of B, length h_out
+  const int64_t* a_start_a;
+  const int64_t* a_loc_a;
+  const int64_t* a_start_b;
+  const int64_t* a_loc_b;
+  int32_t h_in;
+  int32_t h_out;
+  int32_t slot_a;
+  int32_t slot_b;
+  int32_t layout_b;
+  int32_t pad_[3];
+};
+
+// ---- groups of rows for the gather mat-vec kernels
+struct BgmvGroups {
+  // gather mode (tiles != nullptr)
+  const int32_t* tiles;
+  const int32_t* gather_rows;
+  const int32_t* counts;      // device counts written by the packer
+  // token mode
+  const int64_t* indicies;
+  int64_t batch;
+  // adapter tables (single-problem calls; a step plan carries its own per problem)
+  const int64_t* a_start;
+  const int64_t* a_len;       // 4 * rank
+  const int64_t* a_loc;
+  int64_t qkvo;
+  // step mode: problem blockIdx.z of the plan; the shrink result of problem p
+  // lives at vbuf + p * vstride elements, row pitch kMaxRank
+  const StepProblem* plan;
+  void* vbuf;
+  int64_t vstride;
+};
+
+// ---- where a CTA's tile comes from
+struct TileSource {
+  // mode 0: the reference's problem table (int64, device)
+  const int64_t* output_counts;
+  const int64_t* rank_counts;
+  const int64_t* lora_ids;
+  const int64_t* start_ids;
+  int64_t num_problems;
+  // mode 1: packed schedule (int32 tile records + device counts)
+  const int32_t* tiles;
+  const int32_t* counts;
+  // adapter tables
+  const int64_t* a_start;
+  const int64_t* a_loc;
+  int64_t slot;                      // qkvo
+  int mode;
+  // step mode: problem blockIdx.z of the plan supplies tensor maps, pointers and
+  // index tables; the shrink result of problem p is vbuf + p * vstride elements
+  // (row pitch kMaxRank)
+  const StepProblem* plan;
+  void* vbuf;
+  int64_t vstride;
+};
+
+// launchers shared between the single-problem entry points and the step entry point
+int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int box_rows);
+int bgmv_gather_launch(void* y, const void* x, const void* w, const void* scales,
+                       const BgmvGroups& groups, int64_t max_groups, int h_in, int h_out,
+                       int layout, int dtype, cudaStream_t stream, int n_problems);
+int atmm_launch(void* y, const void* x, const void* w, const void* scales, const TileSource& src,
+                int64_t max_tiles, int64_t T_rows, int h_in, int h_out, int64_t w_cells, int dtype,
+                int flags, cudaStream_t stream, int n_problems);
+
+}  // namespace vlr

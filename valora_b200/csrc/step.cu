@@ -1,0 +1,101 @@
+// One step over many LoRA projections: the step plan (per-problem tensor maps
+// and pointers in device memory) and the four batched launches that run the
+// shrink and the expand of every problem of a packed batch.
+#include <string.h>
+
+#include "common.cuh"
+#include "problem.cuh"
+
+using namespace vlr;
+
+extern "C" size_t vlr_step_plan_bytes(int n_problems) {
+  return n_problems > 0 ? (size_t)n_problems * sizeof(StepProblem) : 0;
+}
+
+extern "C" int vlr_step_plan_build(const vlr_problem_t* problems, int n_problems, int64_t max_rows,
+                                   int dtype, void* plan_host) {
+  if (!problems || !plan_host) return VLR_ERR_NULL;
+  if (n_problems <= 0 || n_problems > 65535 || max_rows <= 0 || max_rows > 0x7fffffff) return VLR_ERR_RANGE;
+  if (dtype != VLR_F16 && dtype != VLR_BF16) return VLR_ERR_DTYPE;
+  StepProblem* out = reinterpret_cast<StepProblem*>(plan_host);
+  for (int i = 0; i < n_problems; ++i) {
+    const vlr_problem_t& p = problems[i];
+    if (!p.x || !p.y || !p.wa || !p.wb || !p.a_start_a || !p.a_loc_a || !p.a_start_b || !p.a_loc_b)
+      return VLR_ERR_NULL;
+    if (p.h_in <= 0 || p.h_out <= 0 || p.h_in >= 65536 || p.h_out >= 65536 || (p.h_in & 7) ||
+        (p.h_out & 7))
+      return VLR_ERR_SHAPE;
+    if (p.cells_a <= 0 || p.cells_b <= 0 || p.slot_a < 0 || p.slot_b < 0) return VLR_ERR_RANGE;
+    if (!aligned16(p.x) || !aligned16(p.y) || !aligned16(p.wa) || !aligned16(p.wb)) return VLR_ERR_ALIGN;
+    StepProblem sp;
+    memset(&sp, 0, sizeof(sp));
+    int rc;
+    if ((rc = make_map_2d(&sp.map_x, p.x, dtype, max_rows, p.h_in, 32)) != VLR_OK) return rc;
+    if ((rc = make_map_2d(&sp.map_wa, p.wa, dtype, p.cells_a, p.h_in, 16)) != VLR_OK) return rc;
+    if ((rc = make_map_2d(&sp.map_y, p.y, dtype, max_rows, p.h_out, 32)) != VLR_OK) return rc;
+    if ((rc = make_map_2d(&sp.map_wb, p.wb, dtype, p.cells_b, p.h_out, 16)) != VLR_OK) return rc;
+    sp.x = p.x; sp.y = p.y; sp.wa = p.wa; sp.wb = p.wb;
+    sp.a_start_a = p.a_start_a; sp.a_loc_a = p.a_loc_a;
+    sp.a_start_b = p.a_start_b; sp.a_loc_b = p.a_loc_b;
+    sp.h_in = p.h_in; sp.h_out = p.h_out; sp.slot_a = p.slot_a; sp.slot_b = p.slot_b;
+    sp.layout_b = VLR_LAYOUT_ROWS;
+    memcpy(&out[i], &sp, sizeof(sp));
+  }
+  return VLR_OK;
+}
+
+extern "C" size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems) {
+  if (T <= 0 || n_problems <= 0) return 256;
+  return (size_t)n_problems * (size_t)T * kMaxRank * 2 + 256;
+}
+
+extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
+                             const int32_t* gather_rows, int64_t max_mma_tiles,
+                             int64_t max_gather_tiles, const int32_t* counts, const void* scales,
+                             int max_h_in, int max_h_out, int dtype, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+  if (T == 0 || n_problems == 0) return VLR_OK;
+  if (!plan_dev || !tiles || !gather_rows || !counts || !scales || !workspace) return VLR_ERR_NULL;
+  if (dtype != VLR_F16 && dtype != VLR_BF16) return VLR_ERR_DTYPE;
+  if (T < 0 || T > 0x7fffffff || n_problems < 0 || n_problems > 65535) return VLR_ERR_RANGE;
+  if (max_h_in <= 0 || max_h_out <= 0 || max_h_in >= 65536 || max_h_out >= 65536) return VLR_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(plan_dev) & 127u) != 0) return VLR_ERR_ALIGN;
+  char* vb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
+  const size_t need = (size_t)n_problems * (size_t)T * kMaxRank * 2;
+  if ((size_t)(vb - reinterpret_cast<char*>(workspace)) + need > workspace_bytes) return VLR_ERR_WORKSPACE;
+  // every tile holds at least one row
+  if (max_mma_tiles <= 0 || max_mma_tiles > T) max_mma_tiles = T;
+  if (max_gather_tiles <= 0 || max_gather_tiles > T) max_gather_tiles = T;
+  cudaStream_t s = (cudaStream_t)stream;
+  const StepProblem* plan = reinterpret_cast<const StepProblem*>(plan_dev);
+
+  TileSource src{};
+  src.mode = 1;
+  src.tiles = tiles;
+  src.counts = counts;
+  src.plan = plan;
+  src.vbuf = vb;
+  src.vstride = T * kMaxRank;
+  BgmvGroups g{};
+  g.tiles = tiles;
+  g.gather_rows = gather_rows;
+  g.counts = counts;
+  g.plan = plan;
+  g.vbuf = vb;
+  g.vstride = T * kMaxRank;
+
+  int rc;
+  // shrink: h_in >= h_out selects it in the launchers
+  rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, max_h_in, kMaxRank, 0,
+                   dtype, 0, s, n_problems);
+  if (rc != VLR_OK) return rc;
+  rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, max_h_in, kMaxRank,
+                          VLR_LAYOUT_ROWS, dtype, s, n_problems);
+  if (rc != VLR_OK) return rc;
+  // expand
+  rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, kMaxRank, max_h_out, 0,
+                   dtype, VLR_ATMM_APPLY_SCALE, s, n_problems);
+  if (rc != VLR_OK) return rc;
+  return bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, kMaxRank,
+                            max_h_out, VLR_LAYOUT_ROWS, dtype, s, n_problems);
+}

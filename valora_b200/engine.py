@@ -1,0 +1,140 @@
+"""LoraStepEngine: the host-side object a serving loop holds.
+
+It owns the adapter pools (one per side and row width), the activation buffers
+of every (layer, projection) problem, the device packer and the step plan, and
+runs one step - pack the batch on the device, then shrink + expand of every
+problem - without touching the host in between.
+
+In the reference the same work is spread over ModelRpcServer.set_sgmm_args
+(valora/server/router/model_infer/model_rpc.py:265-374, host packing),
+InferAdapter (valora/server/router/model_infer/infer_adapter.py:94-173, pool
+tables) and LoraUnorderedBatchInfer._lora_get_qkv / _lora_get_o
+(valora/models/peft/lora_unordered_batch_infer.py:876-1071, 1563-1683: 6-8
+operator calls per layer, each followed by a host synchronisation).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import ops
+from .pool import AdapterPool
+
+
+class LoraStepEngine:
+    def __init__(self, projections: Sequence[Tuple[str, int, int]], ranks: Sequence[int],
+                 scalings: Sequence[float], dtype, device, layers: int, max_tokens: int,
+                 tile_m: int = 128, mma_min_rows: int = 16, gather_rows_per_tile: int = 8,
+                 alloc_activations: bool = True):
+        self.projections = list(projections)
+        self.ranks = [int(r) for r in ranks]
+        self.dtype, self.device = dtype, torch.device(device)
+        self.layers, self.max_tokens = int(layers), int(max_tokens)
+        n_ad = len(self.ranks)
+        # slot maps: projection p -> (width, slot) on each side
+        self.slot_a: Dict[int, Tuple[int, int]] = {}
+        self.slot_b: Dict[int, Tuple[int, int]] = {}
+        na: Dict[int, int] = {}
+        nb: Dict[int, int] = {}
+        for p, (_, hi, ho) in enumerate(self.projections):
+            self.slot_a[p] = (hi, na.get(hi, 0))
+            na[hi] = na.get(hi, 0) + 1
+            self.slot_b[p] = (ho, nb.get(ho, 0))
+            nb[ho] = nb.get(ho, 0) + 1
+        tot_rank = sum(self.ranks)
+        self.pool_a = {w: AdapterPool(tot_rank * n + 16, w, n, dtype, self.device, self.layers) for w, n in na.items()}
+        self.pool_b = {w: AdapterPool(tot_rank * n + 16, w, n, dtype, self.device, self.layers) for w, n in nb.items()}
+        for a in range(n_ad):
+            for pools in (self.pool_a, self.pool_b):
+                for pool in pools.values():
+                    pool.load_adapter(f"adapter{a}", self.ranks[a], float(scalings[a]),
+                                      [[None] * pool.n_slots for _ in range(self.layers)])
+        any_pool = next(iter(self.pool_a.values()))
+        self.a_len = any_pool.a_len
+        self.scales = any_pool.a_scaling
+        self.packer = ops.Packer(self.max_tokens, n_ad, self.device, tile_m, mma_min_rows, gather_rows_per_tile)
+        self.x: List[List[torch.Tensor]] = []
+        self.y: List[List[torch.Tensor]] = []
+        self.plan: Optional[ops.StepPlan] = None
+        if alloc_activations:
+            for _ in range(self.layers):
+                self.x.append([torch.zeros((self.max_tokens, hi), dtype=dtype, device=self.device)
+                               for _, hi, _ in self.projections])
+                self.y.append([torch.zeros((self.max_tokens, ho), dtype=dtype, device=self.device)
+                               for _, _, ho in self.projections])
+            self.build_plan()
+
+    # ---- weights
+    def set_adapter_weights(self, layer: int, proj: int, adapter: int, A: torch.Tensor, B: torch.Tensor):
+        """A [h_in, r] and B [r, h_out] of one adapter for one projection."""
+        r = self.ranks[adapter]
+        wa, sa = self.slot_a[proj]
+        wb, sb = self.slot_b[proj]
+        pa, pb = self.pool_a[wa], self.pool_b[wb]
+        ca = pa.a_loc[pa.a_start[adapter] + r * sa: pa.a_start[adapter] + r * (sa + 1)]
+        cb = pb.a_loc[pb.a_start[adapter] + r * sb: pb.a_start[adapter] + r * (sb + 1)]
+        pa.buffer[layer][ca] = A.to(device=self.device, dtype=self.dtype).T.contiguous()
+        pb.buffer[layer][cb] = B.to(device=self.device, dtype=self.dtype)
+
+    def randomize_weights(self, seed: int = 0, std: float = 0.02):
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        for pools in (self.pool_a, self.pool_b):
+            for pool in pools.values():
+                for layer in range(self.layers):
+                    buf = pool.buffer[layer]
+                    buf.copy_((torch.randn(buf.shape, generator=g, device=self.device, dtype=torch.float32) * std).to(self.dtype))
+
+    def adapter_weights(self, layer: int, proj: int, adapter: int):
+        """(A [h_in, r], B [r, h_out]) read back from the pools."""
+        r = self.ranks[adapter]
+        wa, sa = self.slot_a[proj]
+        wb, sb = self.slot_b[proj]
+        pa, pb = self.pool_a[wa], self.pool_b[wb]
+        ca = pa.a_loc[pa.a_start[adapter] + r * sa: pa.a_start[adapter] + r * (sa + 1)]
+        cb = pb.a_loc[pb.a_start[adapter] + r * sb: pb.a_start[adapter] + r * (sb + 1)]
+        return pa.buffer[layer][ca].T.contiguous(), pb.buffer[layer][cb].contiguous()
+
+    # ---- plan
+    def build_plan(self):
+        problems = []
+        for layer in range(self.layers):
+            for p in range(len(self.projections)):
+                wa, sa = self.slot_a[p]
+                wb, sb = self.slot_b[p]
+                pa, pb = self.pool_a[wa], self.pool_b[wb]
+                problems.append(ops.Problem(self.x[layer][p], self.y[layer][p], pa.buffer[layer],
+                                            pb.buffer[layer], pa.a_start, pa.a_loc, pb.a_start,
+                                            pb.a_loc, sa, sb))
+        self.plan = ops.StepPlan(problems, self.max_tokens)
+
+    # ---- one step, inputs resident in HBM
+    def step(self, tok_adapter: torch.Tensor, max_mma_tiles: int = 0, max_gather_tiles: int = 0):
+        packed = self.packer.pack(tok_adapter, self.a_len, sort=True)
+        self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles)
+        return packed
+
+    # ---- one step from host buffers (pinned): H2D, step, D2H
+    def step_host(self, tok_adapter_host: torch.Tensor, x_host: Sequence[Sequence[torch.Tensor]],
+                  y_host: Sequence[Sequence[torch.Tensor]], tok_dev: torch.Tensor,
+                  max_mma_tiles: int = 0, max_gather_tiles: int = 0):
+        """x_host[layer][p] / y_host[layer][p] are pinned host tensors of T rows;
+        y_host is read as Y0 and overwritten with Y.  Returns bytes copied
+        (h2d, d2h).  All copies and kernels are enqueued on the current stream."""
+        T = tok_adapter_host.numel()
+        h2d = d2h = 0
+        tok_dev[:T].copy_(tok_adapter_host, non_blocking=True)
+        h2d += T * 8
+        for layer in range(self.layers):
+            for p in range(len(self.projections)):
+                self.x[layer][p][:T].copy_(x_host[layer][p][:T], non_blocking=True)
+                self.y[layer][p][:T].copy_(y_host[layer][p][:T], non_blocking=True)
+                h2d += x_host[layer][p][:T].numel() * 2 + y_host[layer][p][:T].numel() * 2
+        self.step(tok_dev[:T], max_mma_tiles, max_gather_tiles)
+        for layer in range(self.layers):
+            for p in range(len(self.projections)):
+                y_host[layer][p][:T].copy_(self.y[layer][p][:T], non_blocking=True)
+                d2h += y_host[layer][p][:T].numel() * 2
+        return h2d, d2h
