@@ -75,3 +75,13 @@ def rand_lora(ranks, h_in, h_out, dtype, n_slots=1, seed=0, wstd=0.02):
     A = [[(torch.randn(h_in, int(r), generator=g) * wstd).to(dtype) for r in ranks] for _ in range(n_slots)]
     B = [[(torch.randn(int(r), h_out, generator=g) * wstd).to(dtype) for r in ranks] for _ in range(n_slots)]
     return A, B
+
+
+def out_tolerance(ref32, dtype, tol=1e-2):
+    """Elementwise bound on |out - ref32| for an output of 16-bit type `dtype`:
+    tol, or - where the output grid itself is coarser - half an ulp of `dtype` at
+    the reference's magnitude (plus a sliver for the fp32 accumulation order)."""
+    prec = 8 if dtype == torch.bfloat16 else 11          # significand bits
+    mag = ref32.abs().clamp_min(1e-30)
+    half_ulp = torch.exp2(torch.floor(torch.log2(mag)) - prec)
+    return torch.maximum(torch.full_like(ref32, tol), half_ulp * 1.01 + 1e-4)

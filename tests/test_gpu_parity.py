@@ -1,13 +1,15 @@
 """GPU parity: the CUDA path through the C ABI against the CPU oracle on the
-same seeded inputs.  Bit-exact for packing and index tables; max-abs error
-<= 1e-2 against the oracle's fp32 result for fp16 / bf16 outputs."""
+same seeded inputs.  Bit-exact for packing and index tables.  Floating point:
+every output element is within 1e-2 of the oracle's fp32 result; where the
+output's own 16-bit grid is coarser than that (bf16 at |y| >= 4 has a half-ulp
+of 0.0156) the bound is the half-ulp of the output type at that magnitude."""
 import numpy as np
 import pytest
 import torch
 
 import oracle
 from valora_b200 import workloads
-from tests.helpers import build_tables, fill_pool_a, fill_pool_b, rand_lora, t64
+from tests.helpers import build_tables, fill_pool_a, fill_pool_b, out_tolerance, rand_lora, t64
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-2
@@ -23,7 +25,12 @@ def ops():
 
 
 def _err(got, ref32):
-    return float((got.float().cpu() - ref32).abs().max())
+    """Largest excess of |got - ref32| over the elementwise tolerance, shifted by
+    TOL so that `_err(...) <= TOL` reads 'every element is within its bound'."""
+    if got.numel() == 0:
+        return 0.0
+    excess = (got.float().cpu() - ref32).abs() - out_tolerance(ref32, got.dtype, TOL)
+    return float(excess.max()) + TOL
 
 
 # --------------------------------------------------------------------------- BGMV
@@ -356,7 +363,10 @@ def _step_case(ops, batch, proj_ids, layers=1, mma_min=16):
             for a in np.unique(batch.tok_adapter):
                 rows = torch.from_numpy(np.nonzero(batch.tok_adapter == a)[0])
                 A, B = W[(layer, p, int(a))]
-                truth[rows] += (xf[rows] @ A.float()) @ B.float() * float(sc[a])
+                # V is kept in a 16-bit buffer between shrink and expand, as in the
+                # reference (its delta buffers are 16-bit tensors)
+                vv = (xf[rows] @ A.float()).to(batch.dtype).float()
+                truth[rows] += (vv @ B.float()) * float(sc[a])
             assert _err(eng.y[layer][p], truth) <= TOL, (layer, p)
     return eng
 

@@ -5,6 +5,9 @@
 //  * gather mode - group g is a gather tile of the packed schedule: up to G rows
 //    of one adapter, listed in gather_rows, so the adapter's rows are fetched
 //    from HBM once per group instead of once per token.
+// Every kernel is a persistent loop over work items (problem, group, slice):
+// the item count may live on the device (the packer's counts), so the grid is
+// sized for the machine, not for the batch.
 // Adapter rows are read with 128-bit loads that bypass L1; partial dot products
 // are reduced with warp shuffles; accumulation is fp32 with a single rounding.
 #include "common.cuh"
@@ -12,7 +15,7 @@
 
 namespace vlr {
 
-// The tensors one CTA works on, from the direct arguments or from the plan.
+// The tensors one work item touches, from the direct arguments or from the plan.
 template <typename T>
 struct ProbView {
   T* y;
@@ -25,12 +28,13 @@ struct ProbView {
 };
 
 template <typename T>
-__device__ __forceinline__ ProbView<T> problem_view(const BgmvGroups& g, T* y, const T* x, const T* w,
-                                                    int h_in, int h_out, bool expand) {
+__device__ __forceinline__ ProbView<T> problem_view(const BgmvGroups& g, int problem, T* y,
+                                                    const T* x, const T* w, int h_in, int h_out,
+                                                    bool expand) {
   ProbView<T> pv;
   if (g.plan != nullptr) {
-    const StepProblem& sp = g.plan[blockIdx.z];
-    T* vb = reinterpret_cast<T*>(g.vbuf) + (int64_t)blockIdx.z * g.vstride;
+    const StepProblem& sp = g.plan[problem];
+    T* vb = reinterpret_cast<T*>(g.vbuf) + (int64_t)problem * g.vstride;
     if (expand) {
       pv.y = reinterpret_cast<T*>(sp.y); pv.x = vb; pv.w = reinterpret_cast<const T*>(sp.wb);
       pv.a_start = sp.a_start_b; pv.a_loc = sp.a_loc_b; pv.slot = sp.slot_b;
@@ -47,334 +51,346 @@ __device__ __forceinline__ ProbView<T> problem_view(const BgmvGroups& g, T* y, c
   return pv;
 }
 
-template <int G>
-struct Group {
-  int adapter, rank, nrows;
+// What one CTA needs to know about its current item; filled by thread 0.
+template <typename T, int G>
+struct Item {
+  ProbView<T> pv;
+  int adapter, rank, nrows, slice;
+  int64_t gbase;                 // a_start[adapter] + rank * slot
+  int rows[G];
 };
 
-// Resolve the calling CTA's group into shared memory.  Returns false if the CTA
-// has no work.  rows[] receives the token rows (G entries, -1 padded).
-template <int G>
-__device__ __forceinline__ bool resolve_group(const BgmvGroups& g, int gid, Group<G>& out,
-                                              int* rows) {
-  if (g.tiles != nullptr) {
-    const int n_gather = g.counts[VLR_COUNT_GATHER_TILES];
-    if (gid >= n_gather) return false;
-    const int32_t* t = g.tiles + (int64_t)(g.counts[VLR_COUNT_MMA_TILES] + gid) * VLR_TILE_INTS;
-    out.adapter = t[1];
-    out.rank = t[2];
-    out.nrows = min(t[4], G);
-    const int first = t[3];
-#pragma unroll
-    for (int i = 0; i < G; ++i) rows[i] = i < out.nrows ? g.gather_rows[first + i] : -1;
-  } else {
-    if (gid >= g.batch) return false;
-    out.adapter = (int)g.indicies[gid];
-    out.rank = (int)(g.a_len[out.adapter] / 4);
-    out.nrows = 1;
-#pragma unroll
-    for (int i = 0; i < G; ++i) rows[i] = i == 0 ? gid : -1;
-  }
-  return true;
+__device__ __forceinline__ int64_t n_groups_of(const BgmvGroups& g) {
+  return g.tiles != nullptr ? (int64_t)g.counts[VLR_COUNT_GATHER_TILES] : g.batch;
 }
 
-constexpr int kShrinkThreads = 256;
-constexpr int kShrinkWarps = kShrinkThreads / 32;
-constexpr int kShrinkRows = 2;                        // rank rows per warp
-constexpr int kShrinkSlice = kShrinkWarps * kShrinkRows;
+// item -> (problem, group, slice); slices vary fastest so that the CTAs working
+// on one group at the same time share its activation rows in L2.
+template <typename T, int G>
+__device__ __forceinline__ void resolve_item(const BgmvGroups& g, int64_t item, int64_t n_groups,
+                                             int n_slices, T* y, const T* x, const T* w, int h_in,
+                                             int h_out, bool expand, Item<T, G>* out) {
+  Item<T, G> it;
+  it.slice = (int)(item % n_slices);
+  const int64_t pg = item / n_slices;
+  const int gid = (int)(pg % n_groups);
+  const int problem = (int)(pg / n_groups);
+  it.pv = problem_view<T>(g, problem, y, x, w, h_in, h_out, expand);
+  if (g.tiles != nullptr) {
+    const int32_t* t = g.tiles + (int64_t)(g.counts[VLR_COUNT_MMA_TILES] + gid) * VLR_TILE_INTS;
+    it.adapter = t[1];
+    it.rank = t[2];
+    it.nrows = min(t[4], G);
+    const int first = t[3];
+#pragma unroll
+    for (int i = 0; i < G; ++i) it.rows[i] = i < it.nrows ? g.gather_rows[first + i] : -1;
+  } else {
+    it.adapter = (int)g.indicies[gid];
+    it.rank = (int)(g.a_len[it.adapter] / 4);
+    it.nrows = 1;
+#pragma unroll
+    for (int i = 0; i < G; ++i) it.rows[i] = i == 0 ? gid : -1;
+  }
+  if (it.rank < 0 || it.rank > kMaxRank) it.rank = 0;
+  it.gbase = it.pv.a_start[it.adapter] + (int64_t)it.rank * it.pv.slot;
+  *out = it;
+}
+
+constexpr int kThreadsBgmv = 256;
+constexpr int kWarpsBgmv = kThreadsBgmv / 32;
 constexpr int kShrinkKB = 2048;                       // activation elements staged per pass
 
 // y[row, j] = sum_k x[row, k] * W[cell(j), k]   for j < rank        (overwrites)
-template <typename T, int G>
-__global__ void __launch_bounds__(kShrinkThreads)
+// R = rank rows per warp; a slice is 8 * R rank rows.
+template <typename T, int G, int R>
+__global__ void __launch_bounds__(kThreadsBgmv)
 bgmv_shrink_kernel(T* __restrict__ y_, const T* __restrict__ x_, const T* __restrict__ w_,
-                   BgmvGroups groups, int h_in_, int y_pitch_) {
-  const ProbView<T> pv = problem_view<T>(groups, y_, x_, w_, h_in_, y_pitch_, false);
-  T* __restrict__ y = pv.y;
-  const T* __restrict__ x = pv.x;
-  const T* __restrict__ w = pv.w;
-  const int h_in = pv.h_in, y_pitch = pv.h_out;
+                   BgmvGroups groups, int h_in_, int y_pitch_, int n_slices, int n_problems) {
   __shared__ __align__(16) T xs[G][kShrinkKB];
-  __shared__ int rows_s[G];
-  __shared__ Group<G> grp_s;
+  __shared__ Item<T, G> item_s;
+  constexpr int kSlice = kWarpsBgmv * R;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-    Group<G> gr;
-    int rows[G];
-    bool ok = resolve_group<G>(groups, blockIdx.x, gr, rows);
-    if (!ok) gr.nrows = 0;
-    grp_s = gr;
-#pragma unroll
-    for (int i = 0; i < G; ++i) rows_s[i] = rows[i];
-  }
-  __syncthreads();
-  const Group<G> gr = grp_s;
-  const int slice0 = blockIdx.y * kShrinkSlice;
-  if (gr.nrows == 0 || slice0 >= gr.rank) return;
-  const int64_t gbase = pv.a_start[gr.adapter] + (int64_t)gr.rank * pv.slot;
+  const int64_t n_groups = n_groups_of(groups);
+  const int64_t total = n_groups * n_slices * n_problems;
 
-  // this warp's rank rows
-  const T* wrow[kShrinkRows];
-  bool live[kShrinkRows];
-#pragma unroll
-  for (int r = 0; r < kShrinkRows; ++r) {
-    const int j = slice0 + warp * kShrinkRows + r;
-    live[r] = j < gr.rank;
-    const int64_t cell = live[r] ? pv.a_loc[gbase + j] : 0;
-    wrow[r] = w + cell * (int64_t)h_in;
-  }
-
-  float acc[kShrinkRows][G];
-#pragma unroll
-  for (int r = 0; r < kShrinkRows; ++r)
-#pragma unroll
-    for (int g = 0; g < G; ++g) acc[r][g] = 0.f;
-
-  for (int kb = 0; kb < h_in; kb += kShrinkKB) {
-    const int kn = min(kShrinkKB, h_in - kb);          // multiple of 8
-    // stage the group's activation rows
-    for (int c = tid; c < G * (kShrinkKB / 8); c += kShrinkThreads) {
-      const int g = c / (kShrinkKB / 8), cc = c % (kShrinkKB / 8);
-      uint4 v = make_uint4(0, 0, 0, 0);
-      const int row = rows_s[g];
-      if (row >= 0 && cc * 8 < kn) v = ldg128_stream(x + (int64_t)row * h_in + kb + cc * 8);
-      *reinterpret_cast<uint4*>(&xs[g][cc * 8]) = v;
-    }
+  for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
+    __syncthreads();                                   // previous item done with item_s / xs
+    if (tid == 0) resolve_item<T, G>(groups, item, n_groups, n_slices, y_, x_, w_, h_in_, y_pitch_, false, &item_s);
     __syncthreads();
-    if (live[0]) {
-      const int nchunk = kn / 8;
-#pragma unroll 4
-      for (int c = lane; c < nchunk; c += 32) {
-        uint4 wv[kShrinkRows];
+    const int rank = item_s.rank, nrows = item_s.nrows;
+    const int slice0 = item_s.slice * kSlice;
+    if (nrows == 0 || slice0 >= rank) continue;
+    const T* __restrict__ x = item_s.pv.x;
+    const T* __restrict__ w = item_s.pv.w;
+    const int h_in = item_s.pv.h_in;
+
+    const T* wrow[R];
+    bool live[R];
 #pragma unroll
-        for (int r = 0; r < kShrinkRows; ++r)
-          wv[r] = live[r] ? ldg128_stream(wrow[r] + kb + c * 8) : make_uint4(0, 0, 0, 0);
-        float wf[kShrinkRows][8];
+    for (int r = 0; r < R; ++r) {
+      const int j = slice0 + warp * R + r;
+      live[r] = j < rank;
+      const int64_t cell = live[r] ? item_s.pv.a_loc[item_s.gbase + j] : 0;
+      wrow[r] = w + cell * (int64_t)h_in;
+    }
+    float acc[R][G];
 #pragma unroll
-        for (int r = 0; r < kShrinkRows; ++r) unpack8<T>(wv[r], wf[r]);
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float xf[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(&xs[g][c * 8]), xf);
+      for (int g = 0; g < G; ++g) acc[r][g] = 0.f;
+
+    for (int kb = 0; kb < h_in; kb += kShrinkKB) {
+      const int kn = min(kShrinkKB, h_in - kb);        // multiple of 8
+      if (kb) __syncthreads();
+      for (int c = tid; c < G * (kShrinkKB / 8); c += kThreadsBgmv) {
+        const int g = c / (kShrinkKB / 8), cc = c % (kShrinkKB / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        const int row = item_s.rows[g];
+        if (row >= 0 && cc * 8 < kn) v = ldg128_stream(x + (int64_t)row * h_in + kb + cc * 8);
+        *reinterpret_cast<uint4*>(&xs[g][cc * 8]) = v;
+      }
+      __syncthreads();
+      if (live[0]) {
+        const int nchunk = kn / 8;
+#pragma unroll 2
+        for (int c = lane; c < nchunk; c += 32) {
+          uint4 wv[R];
 #pragma unroll
-          for (int r = 0; r < kShrinkRows; ++r)
+          for (int r = 0; r < R; ++r)
+            wv[r] = live[r] ? ldg128_stream(wrow[r] + kb + c * 8) : make_uint4(0, 0, 0, 0);
+          float xf[G][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[r][g] = fmaf(wf[r][e], xf[e], acc[r][g]);
+          for (int g = 0; g < G; ++g) unpack8<T>(*reinterpret_cast<const uint4*>(&xs[g][c * 8]), xf[g]);
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            float wf[8];
+            unpack8<T>(wv[r], wf);
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[r][g] = fmaf(wf[e], xf[g][e], acc[r][g]);
+          }
         }
       }
     }
-    __syncthreads();
-  }
-
+    T* __restrict__ y = item_s.pv.y;
+    const int y_pitch = item_s.pv.h_out;
 #pragma unroll
-  for (int r = 0; r < kShrinkRows; ++r)
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float s = warp_sum(acc[r][g]);
-      if (lane == 0 && live[r] && g < gr.nrows) {
-        const int j = slice0 + warp * kShrinkRows + r;
-        y[(int64_t)rows_s[g] * y_pitch + j] = Elem<T>::from_float(s);
+      for (int g = 0; g < G; ++g) {
+        const float s = warp_sum(acc[r][g]);
+        if (lane == 0 && live[r] && g < nrows) {
+          const int j = slice0 + warp * R + r;
+          y[(int64_t)item_s.rows[g] * y_pitch + j] = Elem<T>::from_float(s);
+        }
       }
-    }
+  }
 }
 
-constexpr int kExpandThreads = 256;
-constexpr int kExpandCols = kExpandThreads * 8;       // outputs per CTA, rows layout
+constexpr int kExpandCols = kThreadsBgmv * 8;         // outputs per item, rows layout
 
 // rows layout: y[row, o] += scale * sum_{k<rank} v[row, k] * B[cell(k), o]
 template <typename T, int G>
-__global__ void __launch_bounds__(kExpandThreads)
+__global__ void __launch_bounds__(kThreadsBgmv)
 bgmv_expand_rows_kernel(T* __restrict__ y_, const T* __restrict__ v_, const T* __restrict__ w_,
-    const T* __restrict__ scales, BgmvGroups groups, int h_out_, int v_pitch_) {
-  const ProbView<T> pv = problem_view<T>(groups, y_, v_, w_, v_pitch_, h_out_, true);
-  T* __restrict__ y = pv.y;
-  const T* __restrict__ v = pv.x;
-  const T* __restrict__ w = pv.w;
-  const int h_out = pv.h_out, v_pitch = pv.h_in;
+                        const T* __restrict__ scales, BgmvGroups groups, int h_out_, int v_pitch_,
+                        int n_slices, int n_problems) {
   __shared__ float vs[G][kMaxRank];
   __shared__ int64_t rowoff[kMaxRank];
-  __shared__ int rows_s[G];
-  __shared__ Group<G> grp_s;
+  __shared__ Item<T, G> item_s;
 
   const int tid = threadIdx.x;
-  if (tid == 0) {
-    Group<G> gr;
-    int rows[G];
-    bool ok = resolve_group<G>(groups, blockIdx.x, gr, rows);
-    if (!ok) gr.nrows = 0;
-    grp_s = gr;
-#pragma unroll
-    for (int i = 0; i < G; ++i) rows_s[i] = rows[i];
-  }
-  __syncthreads();
-  const Group<G> gr = grp_s;
-  if (gr.nrows == 0 || gr.rank == 0) return;
-  const int64_t gbase = pv.a_start[gr.adapter] + (int64_t)gr.rank * pv.slot;
-  const float scale = Elem<T>::to_float(scales[gr.adapter]);
-  for (int i = tid; i < G * kMaxRank; i += kExpandThreads) {
-    const int g = i / kMaxRank, k = i % kMaxRank;
-    float val = 0.f;
-    if (g < gr.nrows && k < gr.rank)
-      val = Elem<T>::to_float(v[(int64_t)rows_s[g] * v_pitch + k]) * scale;
-    vs[g][k] = val;
-  }
-  for (int k = tid; k < gr.rank; k += kExpandThreads)
-    rowoff[k] = pv.a_loc[gbase + k] * (int64_t)h_out;
-  __syncthreads();
+  const int64_t n_groups = n_groups_of(groups);
+  const int64_t total = n_groups * n_slices * n_problems;
 
-  const int o = (blockIdx.y * kExpandThreads + tid) * 8;
-  if (o >= h_out) return;
+  for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
+    __syncthreads();
+    if (tid == 0) resolve_item<T, G>(groups, item, n_groups, n_slices, y_, v_, w_, v_pitch_, h_out_, true, &item_s);
+    __syncthreads();
+    const int rank = item_s.rank, nrows = item_s.nrows;
+    const int h_out = item_s.pv.h_out, v_pitch = item_s.pv.h_in;
+    const int o = (item_s.slice * kThreadsBgmv + tid) * 8;
+    if (nrows == 0 || rank == 0 || item_s.slice * kExpandCols >= h_out) continue;
+    const T* __restrict__ v = item_s.pv.x;
+    const T* __restrict__ w = item_s.pv.w;
+    const float scale = Elem<T>::to_float(scales[item_s.adapter]);
+    for (int i = tid; i < G * kMaxRank; i += kThreadsBgmv) {
+      const int g = i / kMaxRank, k = i % kMaxRank;
+      float val = 0.f;
+      if (g < nrows && k < rank) val = Elem<T>::to_float(v[(int64_t)item_s.rows[g] * v_pitch + k]) * scale;
+      vs[g][k] = val;
+    }
+    for (int k = tid; k < rank; k += kThreadsBgmv)
+      rowoff[k] = item_s.pv.a_loc[item_s.gbase + k] * (int64_t)h_out;
+    __syncthreads();
+    if (o >= h_out) continue;
 
-  float acc[G][8];
+    float acc[G][8];
 #pragma unroll
-  for (int g = 0; g < G; ++g)
+    for (int g = 0; g < G; ++g)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+      for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
 
-  for (int k0 = 0; k0 < gr.rank; k0 += 8) {           // rank is a multiple of 8
-    uint4 wv[8];
+    for (int k0 = 0; k0 < rank; k0 += 8) {             // rank is a multiple of 8
+      uint4 wv[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) wv[u] = ldg128_stream(w + rowoff[k0 + u] + o);
+      for (int u = 0; u < 8; ++u) wv[u] = ldg128_stream(w + rowoff[k0 + u] + o);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      float wf[8];
-      unpack8<T>(wv[u], wf);
+      for (int u = 0; u < 8; ++u) {
+        float wf[8];
+        unpack8<T>(wv[u], wf);
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float vv = vs[g][k0 + u];
+        for (int g = 0; g < G; ++g) {
+          const float vv = vs[g][k0 + u];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(vv, wf[e], acc[g][e]);
+          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(vv, wf[e], acc[g][e]);
+        }
       }
     }
-  }
+    T* __restrict__ y = item_s.pv.y;
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (g < gr.nrows) {
-      T* yp = y + (int64_t)rows_s[g] * h_out + o;
-      float yf[8];
-      unpack8<T>(ldg128(yp), yf);
+    for (int g = 0; g < G; ++g) {
+      if (g < nrows) {
+        T* yp = y + (int64_t)item_s.rows[g] * h_out + o;
+        float yf[8];
+        unpack8<T>(ldg128(yp), yf);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) yf[e] += acc[g][e];
-      stg128(yp, pack8<T>(yf));
+        for (int e = 0; e < 8; ++e) yf[e] += acc[g][e];
+        stg128(yp, pack8<T>(yf));
+      }
     }
   }
 }
 
-constexpr int kPunicaCols = 256;                      // outputs per CTA, punica layout
+constexpr int kPunicaCols = 256;                      // outputs per item, punica layout
 
 // punica layout: the slot's cells hold the flat bytes of Bt [h_out, rank]:
 // element (o, k) is flat f = o*rank + k, in cell f / h_out at offset f % h_out.
 template <typename T, int G>
-__global__ void __launch_bounds__(kExpandThreads)
+__global__ void __launch_bounds__(kThreadsBgmv)
 bgmv_expand_punica_kernel(T* __restrict__ y_, const T* __restrict__ v_, const T* __restrict__ w_,
-    const T* __restrict__ scales, BgmvGroups groups, int h_out_, int v_pitch_) {
-  const ProbView<T> pv = problem_view<T>(groups, y_, v_, w_, v_pitch_, h_out_, true);
-  T* __restrict__ y = pv.y;
-  const T* __restrict__ v = pv.x;
-  const T* __restrict__ w = pv.w;
-  const int h_out = pv.h_out, v_pitch = pv.h_in;
+                          const T* __restrict__ scales, BgmvGroups groups, int h_out_, int v_pitch_,
+                          int n_slices, int n_problems) {
   __shared__ float vs[G][kMaxRank];
   __shared__ int64_t rowoff[kMaxRank];
-  __shared__ int rows_s[G];
-  __shared__ Group<G> grp_s;
+  __shared__ Item<T, G> item_s;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-    Group<G> gr;
-    int rows[G];
-    bool ok = resolve_group<G>(groups, blockIdx.x, gr, rows);
-    if (!ok) gr.nrows = 0;
-    grp_s = gr;
-#pragma unroll
-    for (int i = 0; i < G; ++i) rows_s[i] = rows[i];
-  }
-  __syncthreads();
-  const Group<G> gr = grp_s;
-  if (gr.nrows == 0 || gr.rank == 0) return;
-  const int64_t gbase = pv.a_start[gr.adapter] + (int64_t)gr.rank * pv.slot;
-  const float scale = Elem<T>::to_float(scales[gr.adapter]);
-  for (int i = tid; i < G * kMaxRank; i += kExpandThreads) {
-    const int g = i / kMaxRank, k = i % kMaxRank;
-    float val = 0.f;
-    if (g < gr.nrows && k < gr.rank)
-      val = Elem<T>::to_float(v[(int64_t)rows_s[g] * v_pitch + k]) * scale;
-    vs[g][k] = val;
-  }
-  for (int k = tid; k < gr.rank; k += kExpandThreads)
-    rowoff[k] = pv.a_loc[gbase + k] * (int64_t)h_out;
-  __syncthreads();
+  const int64_t n_groups = n_groups_of(groups);
+  const int64_t total = n_groups * n_slices * n_problems;
 
-  // lanes per output: next power of two of rank/8 (1..16)
-  const int chunks = gr.rank / 8;
-  int lpo = 1;
-  while (lpo < chunks) lpo <<= 1;
-  const int opw = 32 / lpo;                           // outputs per warp pass
-  const int kc = lane % lpo, ol = lane / lpo;
-  const bool kvalid = kc < chunks;
-  const int o_begin = blockIdx.y * kPunicaCols;
-  const int o_end = min(o_begin + kPunicaCols, h_out);
-
-  for (int o = o_begin + warp * opw + ol; o - ol < o_end; o += (kExpandThreads / 32) * opw) {
-    const bool valid = kvalid && o < o_end;
-    float part[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) part[g] = 0.f;
-    if (valid) {
-      const int64_t f = (int64_t)o * gr.rank + kc * 8;
-      const int bin = (int)(f / h_out), off = (int)(f % h_out);
-      float wf[8];
-      unpack8<T>(ldg128_stream(w + rowoff[bin] + off), wf);
-#pragma unroll
-      for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) part[g] = fmaf(vs[g][kc * 8 + e], wf[e], part[g]);
+  for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
+    __syncthreads();
+    if (tid == 0) resolve_item<T, G>(groups, item, n_groups, n_slices, y_, v_, w_, v_pitch_, h_out_, true, &item_s);
+    __syncthreads();
+    const int rank = item_s.rank, nrows = item_s.nrows;
+    const int h_out = item_s.pv.h_out, v_pitch = item_s.pv.h_in;
+    const int o_begin = item_s.slice * kPunicaCols;
+    if (nrows == 0 || rank == 0 || o_begin >= h_out) continue;
+    const T* __restrict__ v = item_s.pv.x;
+    const T* __restrict__ w = item_s.pv.w;
+    const float scale = Elem<T>::to_float(scales[item_s.adapter]);
+    for (int i = tid; i < G * kMaxRank; i += kThreadsBgmv) {
+      const int g = i / kMaxRank, k = i % kMaxRank;
+      float val = 0.f;
+      if (g < nrows && k < rank) val = Elem<T>::to_float(v[(int64_t)item_s.rows[g] * v_pitch + k]) * scale;
+      vs[g][k] = val;
     }
+    for (int k = tid; k < rank; k += kThreadsBgmv)
+      rowoff[k] = item_s.pv.a_loc[item_s.gbase + k] * (int64_t)h_out;
+    __syncthreads();
+
+    // lanes per output: next power of two of rank/8 (1..16)
+    const int chunks = rank / 8;
+    int lpo = 1;
+    while (lpo < chunks) lpo <<= 1;
+    const int opw = 32 / lpo;                         // outputs per warp pass
+    const int kc = lane % lpo, ol = lane / lpo;
+    const bool kvalid = kc < chunks;
+    const int o_end = min(o_begin + kPunicaCols, h_out);
+    T* __restrict__ y = item_s.pv.y;
+
+    for (int o = o_begin + warp * opw + ol; o - ol < o_end; o += kWarpsBgmv * opw) {
+      const bool valid = kvalid && o < o_end;
+      float part[G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = part[g];
-      for (int d = lpo >> 1; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-      if (kc == 0 && o < o_end && g < gr.nrows) {
-        T* yp = y + (int64_t)rows_s[g] * h_out + o;
-        *yp = Elem<T>::from_float(Elem<T>::to_float(*yp) + s);
+      for (int g = 0; g < G; ++g) part[g] = 0.f;
+      if (valid) {
+        const int64_t f = (int64_t)o * rank + kc * 8;
+        const int bin = (int)(f / h_out), off = (int)(f % h_out);
+        float wf[8];
+        unpack8<T>(ldg128_stream(w + rowoff[bin] + off), wf);
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) part[g] = fmaf(vs[g][kc * 8 + e], wf[e], part[g]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float s = part[g];
+        for (int d = lpo >> 1; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+        if (kc == 0 && o < o_end && g < nrows) {
+          T* yp = y + (int64_t)item_s.rows[g] * h_out + o;
+          *yp = Elem<T>::from_float(Elem<T>::to_float(*yp) + s);
+        }
       }
     }
   }
 }
 
-// In step mode (groups.plan set) h_in / h_out are the maxima over the plan's
-// problems (they size grid.y) and n_problems is grid.z.
-template <typename T, int G>
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
+// max_groups is a host-side upper bound of the group count (exact in token
+// mode); in step mode (groups.plan set) h_in / h_out are maxima over the plan.
+template <typename T, int G, int R>
 int launch_bgmv(T* y, const T* x, const T* w, const T* scales, const BgmvGroups& groups,
-                int64_t n_groups, int h_in, int h_out, int layout, cudaStream_t stream,
-                int n_problems = 1) {
-  if (n_groups <= 0 || n_problems <= 0) return VLR_OK;
+                int64_t max_groups, int h_in, int h_out, int layout, cudaStream_t stream,
+                int n_problems) {
+  if (max_groups <= 0 || n_problems <= 0) return VLR_OK;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  auto grid_for = [&](int n_slices) {
+    const int64_t items = max_groups * n_slices * n_problems;
+    return (unsigned)(items < cap ? items : cap);
+  };
   if (h_in >= h_out) {
-    dim3 grid((unsigned)n_groups, (h_out + kShrinkSlice - 1) / kShrinkSlice, n_problems);
-    bgmv_shrink_kernel<T, G><<<grid, kShrinkThreads, 0, stream>>>(y, x, w, groups, h_in, h_out);
+    const int n_slices = (h_out + kWarpsBgmv * R - 1) / (kWarpsBgmv * R);
+    bgmv_shrink_kernel<T, G, R><<<grid_for(n_slices), kThreadsBgmv, 0, stream>>>(
+        y, x, w, groups, h_in, h_out, n_slices, n_problems);
   } else if (layout == VLR_LAYOUT_ROWS) {
-    dim3 grid((unsigned)n_groups, (h_out + kExpandCols - 1) / kExpandCols, n_problems);
-    bgmv_expand_rows_kernel<T, G><<<grid, kExpandThreads, 0, stream>>>(y, x, w, scales, groups,
-                                                                      h_out, h_in);
+    const int n_slices = (h_out + kExpandCols - 1) / kExpandCols;
+    bgmv_expand_rows_kernel<T, G><<<grid_for(n_slices), kThreadsBgmv, 0, stream>>>(
+        y, x, w, scales, groups, h_out, h_in, n_slices, n_problems);
   } else {
-    dim3 grid((unsigned)n_groups, (h_out + kPunicaCols - 1) / kPunicaCols, n_problems);
-    bgmv_expand_punica_kernel<T, G><<<grid, kExpandThreads, 0, stream>>>(y, x, w, scales, groups,
-                                                                        h_out, h_in);
+    const int n_slices = (h_out + kPunicaCols - 1) / kPunicaCols;
+    bgmv_expand_punica_kernel<T, G><<<grid_for(n_slices), kThreadsBgmv, 0, stream>>>(
+        y, x, w, scales, groups, h_out, h_in, n_slices, n_problems);
   }
   return launch_status();
 }
 
-// Used by the step-level entry point (gather mode, G = 8).
+// Used by the step-level entry point (gather mode, 8 rows per group, 64-row slices).
 int bgmv_gather_launch(void* y, const void* x, const void* w, const void* scales,
                        const BgmvGroups& groups, int64_t max_groups, int h_in, int h_out,
                        int layout, int dtype, cudaStream_t stream, int n_problems) {
   if (dtype == VLR_F16)
-    return launch_bgmv<__half, 8>((__half*)y, (const __half*)x, (const __half*)w,
-                                  (const __half*)scales, groups, max_groups, h_in, h_out, layout,
-                                  stream, n_problems);
-  return launch_bgmv<__nv_bfloat16, 8>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,
-                                       (const __nv_bfloat16*)w, (const __nv_bfloat16*)scales,
-                                       groups, max_groups, h_in, h_out, layout, stream, n_problems);
+    return launch_bgmv<__half, 8, 8>((__half*)y, (const __half*)x, (const __half*)w,
+                                     (const __half*)scales, groups, max_groups, h_in, h_out,
+                                     layout, stream, n_problems);
+  return launch_bgmv<__nv_bfloat16, 8, 8>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,
+                                          (const __nv_bfloat16*)w, (const __nv_bfloat16*)scales,
+                                          groups, max_groups, h_in, h_out, layout, stream,
+                                          n_problems);
 }
 
 }  // namespace vlr
@@ -405,10 +421,11 @@ extern "C" int vlr_bgmv(void* y, const void* x, const void* w, const int64_t* a_
   g.qkvo = qkvo;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == VLR_F16)
-    return launch_bgmv<__half, 1>((__half*)y, (const __half*)x, (const __half*)w,
-                                  (const __half*)lora_scales, g, batch, (int)h_in, (int)h_out,
-                                  layout, s);
-  return launch_bgmv<__nv_bfloat16, 1>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,
-                                       (const __nv_bfloat16*)w, (const __nv_bfloat16*)lora_scales,
-                                       g, batch, (int)h_in, (int)h_out, layout, s);
+    return launch_bgmv<__half, 1, 2>((__half*)y, (const __half*)x, (const __half*)w,
+                                     (const __half*)lora_scales, g, batch, (int)h_in, (int)h_out,
+                                     layout, s, 1);
+  return launch_bgmv<__nv_bfloat16, 1, 2>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,
+                                          (const __nv_bfloat16*)w,
+                                          (const __nv_bfloat16*)lora_scales, g, batch, (int)h_in,
+                                          (int)h_out, layout, s, 1);
 }

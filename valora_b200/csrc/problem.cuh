@@ -73,7 +73,13 @@ struct TileSource {
   const StepProblem* plan;
   void* vbuf;
   int64_t vstride;
+  // work decomposition, filled by the launcher
+  int64_t max_tiles;                 // mode 0: upper bound of the tile count
+  int n_problems;
+  int nsplit;                        // expand: work items per tile (column shares)
 };
+
+int sm_count();
 
 // launchers shared between the single-problem entry points and the step entry point
 int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int box_rows);
