@@ -198,11 +198,18 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
  * host-side upper bounds used to size the grids (surplus CTAs exit at once);
  * pass <= 0 for the safe bounds derived from T.  scales: dtype[n_adapters].
  * max_h_in / max_h_out: the largest h_in / h_out over the plan's problems.
+ * phase_mask: which of the four launches to enqueue (VLR_PHASE_ALL for a step;
+ * single phases let a harness time each kernel on its own).
  */
+#define VLR_PHASE_SHRINK_MMA 1
+#define VLR_PHASE_SHRINK_GATHER 2
+#define VLR_PHASE_EXPAND_MMA 4
+#define VLR_PHASE_EXPAND_GATHER 8
+#define VLR_PHASE_ALL 15
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
                   const int32_t* counts, const void* scales, int max_h_in, int max_h_out,
-                  int dtype, void* workspace, size_t workspace_bytes, void* stream);
+                  int dtype, int phase_mask, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -52,8 +52,8 @@ extern "C" size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems) {
 extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                              const int32_t* gather_rows, int64_t max_mma_tiles,
                              int64_t max_gather_tiles, const int32_t* counts, const void* scales,
-                             int max_h_in, int max_h_out, int dtype, void* workspace,
-                             size_t workspace_bytes, void* stream) {
+                             int max_h_in, int max_h_out, int dtype, int phase_mask,
+                             void* workspace, size_t workspace_bytes, void* stream) {
   if (T == 0 || n_problems == 0) return VLR_OK;
   if (!plan_dev || !tiles || !gather_rows || !counts || !scales || !workspace) return VLR_ERR_NULL;
   if (dtype != VLR_F16 && dtype != VLR_BF16) return VLR_ERR_DTYPE;
@@ -84,18 +84,23 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   g.vbuf = vb;
   g.vstride = T * kMaxRank;
 
-  int rc;
+  int rc = VLR_OK;
   // shrink: h_in >= h_out selects it in the launchers
-  rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, max_h_in, kMaxRank, 0,
-                   dtype, 0, s, n_problems);
+  if (phase_mask & VLR_PHASE_SHRINK_MMA)
+    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, max_h_in, kMaxRank, 0,
+                     dtype, 0, s, n_problems);
   if (rc != VLR_OK) return rc;
-  rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, max_h_in, kMaxRank,
-                          VLR_LAYOUT_ROWS, dtype, s, n_problems);
+  if (phase_mask & VLR_PHASE_SHRINK_GATHER)
+    rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, max_h_in,
+                            kMaxRank, VLR_LAYOUT_ROWS, dtype, s, n_problems);
   if (rc != VLR_OK) return rc;
   // expand
-  rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, kMaxRank, max_h_out, 0,
-                   dtype, VLR_ATMM_APPLY_SCALE, s, n_problems);
+  if (phase_mask & VLR_PHASE_EXPAND_MMA)
+    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, kMaxRank, max_h_out, 0,
+                     dtype, VLR_ATMM_APPLY_SCALE, s, n_problems);
   if (rc != VLR_OK) return rc;
-  return bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, kMaxRank,
+  if (phase_mask & VLR_PHASE_EXPAND_GATHER)
+    rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, kMaxRank,
                             max_h_out, VLR_LAYOUT_ROWS, dtype, s, n_problems);
+  return rc;
 }

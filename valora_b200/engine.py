@@ -116,6 +116,18 @@ class LoraStepEngine:
         self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles)
         return packed
 
+    def step_timed(self, tok_adapter: torch.Tensor, events):
+        """Same work as step(), with a CUDA event recorded on the current stream
+        before the packer and after each of the five stages (events: 6 entries)."""
+        events[0].record()
+        packed = self.packer.pack(tok_adapter, self.a_len, sort=True)
+        events[1].record()
+        for i, phase in enumerate((ops.PHASE_SHRINK_MMA, ops.PHASE_SHRINK_GATHER,
+                                   ops.PHASE_EXPAND_MMA, ops.PHASE_EXPAND_GATHER)):
+            self.plan.run(packed, self.scales, 0, 0, phase_mask=phase)
+            events[2 + i].record()
+        return packed
+
     # ---- one step from host buffers (pinned): H2D, step, D2H
     def step_host(self, tok_adapter_host: torch.Tensor, x_host: Sequence[Sequence[torch.Tensor]],
                   y_host: Sequence[Sequence[torch.Tensor]], tok_dev: torch.Tensor,

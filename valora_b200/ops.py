@@ -17,6 +17,7 @@ LAYOUT_PUNICA, LAYOUT_ROWS = 0, 1
 ATMM_ACCUMULATE_SHRINK, ATMM_APPLY_SCALE = 1, 2
 TILE_INTS, COUNT_INTS = 8, 8
 MAX_RANK = 128
+PHASE_SHRINK_MMA, PHASE_SHRINK_GATHER, PHASE_EXPAND_MMA, PHASE_EXPAND_GATHER, PHASE_ALL = 1, 2, 4, 8, 15
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -290,7 +291,7 @@ class StepPlan:
         return self._ws
 
     def run(self, packed: Packed, scales: torch.Tensor, max_mma_tiles: int = 0,
-            max_gather_tiles: int = 0):
+            max_gather_tiles: int = 0, phase_mask: int = PHASE_ALL):
         """Enqueue shrink + expand of every problem for the packed batch."""
         _check_input(scales, "scales")
         if scales.dtype != self.dtype:
@@ -302,7 +303,7 @@ class StepPlan:
                                     _ptr(packed.gather_rows), int(max_mma_tiles),
                                     int(max_gather_tiles), _ptr(packed.counts), _ptr(scales),
                                     self.max_h_in, self.max_h_out,
-                                    F16 if self.dtype == torch.float16 else BF16, _ptr(ws),
+                                    F16 if self.dtype == torch.float16 else BF16, int(phase_mask), _ptr(ws),
                                     ws.numel(), _stream(self.device))
         _lib.check(rc, "vlr_lora_step")
 
