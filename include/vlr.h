@@ -34,6 +34,7 @@ extern "C" {
 #define VLR_ERR_RANGE -6         /* a count or capacity is out of range */
 #define VLR_ERR_DRIVER -7        /* tensor-map encoding is unavailable or failed */
 #define VLR_ERR_UNSUPPORTED -8   /* valid request this build does not implement */
+#define VLR_ERR_STATIC_LIMIT -9  /* batch larger than the built-in scratch of vlr_pack_static */
 
 #define VLR_F16 0
 #define VLR_BF16 1
@@ -134,6 +135,30 @@ int vlr_pack(const int64_t* tok_adapter, int64_t T, const int64_t* a_len, int64_
              int32_t* perm, int64_t* seg_len, int64_t* seg_rank, int64_t* seg_adapter,
              int64_t* seg_start, int32_t* tiles, int64_t tiles_cap, int32_t* gather_rows,
              int32_t* counts, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * vlr_pack with no scratch argument.  No counterpart in the reference (its
+ * host packer allocates fresh CUDA tensors on every forward,
+ * valora/server/router/req_queue.py:35-42).
+ *
+ * For callers that cannot supply device scratch: a step that runs after the
+ * serving pool has claimed the GPU's remaining memory, or host code behind an
+ * FFI that has no allocator and must not provoke the device synchronisation an
+ * allocation implies.  The scratch is a 1 MiB array inside the library's device
+ * image (every GPU that loads the library carries it until the process ends).
+ * Same arguments, outputs and results as vlr_pack, bit for bit.
+ * Limits: T <= 8192 and n_adapters <= 1024, else VLR_ERR_STATIC_LIMIT.
+ * The array is shared by all calls on a device and not cleared between them
+ * (the packer writes everything before reading it); calls whose kernels overlap
+ * on the GPU race on it - keep them on one stream.  The first call on a device
+ * resolves the array's address (cudaGetSymbolAddress) and should be made before
+ * any stream capture starts.  The call allocates nothing.
+ */
+int vlr_pack_static(const int64_t* tok_adapter, int64_t T, const int64_t* a_len, int64_t n_adapters,
+                    int sort, int tile_m, int mma_min_rows, int gather_rows_per_tile,
+                    int32_t* perm, int64_t* seg_len, int64_t* seg_rank, int64_t* seg_adapter,
+                    int64_t* seg_start, int32_t* tiles, int64_t tiles_cap, int32_t* gather_rows,
+                    int32_t* counts, void* stream);
 
 /*
  * Index-table compaction after adapters are offloaded.  Replaces

@@ -28,6 +28,8 @@ _SIGS = {
     "vlr_pack_workspace_bytes": (c_sz, [c_i64, c_i64]),
     "vlr_pack": (c_int, [c_vp, c_i64, c_vp, c_i64, c_int, c_int, c_int, c_int,
                          c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp, c_sz, c_vp]),
+    "vlr_pack_static": (c_int, [c_vp, c_i64, c_vp, c_i64, c_int, c_int, c_int, c_int,
+                                c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_vp, c_vp]),
     "vlr_var_len_copy": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp]),
     "vlr_step_plan_bytes": (c_sz, [c_int]),
     "vlr_step_plan_build": (c_int, [c_vp, c_int, c_i64, c_int, c_vp]),

@@ -19,6 +19,8 @@ extern "C" const char* vlr_error_string(int code) {
     case VLR_ERR_RANGE: return "a count or capacity is out of range";
     case VLR_ERR_DRIVER: return "tensor-map encoding unavailable or failed";
     case VLR_ERR_UNSUPPORTED: return "not implemented in this build";
+    case VLR_ERR_STATIC_LIMIT:
+      return "batch exceeds the built-in scratch of vlr_pack_static (at most 8192 tokens and 1024 adapters)";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -8,6 +8,8 @@
 //   3. pack_scatter  stable placement: perm and the sorted key array
 //   4. pack_tiles    segments, chunks and the tile schedule (one CTA)
 // In reference order (sort = 0) only the last one runs.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace vlr {
@@ -364,4 +366,96 @@ extern "C" int vlr_var_len_copy(const int64_t* old_start, const int64_t* len,
   vlr::var_len_copy_kernel<<<(unsigned)n, 256, 0, (cudaStream_t)stream>>>(old_start, len, old_loc,
                                                                          new_start, new_loc);
   return vlr::launch_status();
+}
+
+// ----------------------------------------------------------------------------
+// vlr_pack_static: the packer for callers that cannot hand over scratch memory.
+//
+// Who that is: a serving step that runs after its memory pool has claimed the
+// device's free HBM (the reference sizes its unified KV/adapter pool from what
+// is left on the GPU, so a later cudaMalloc can simply fail), and host code
+// reached through an FFI that owns no allocator handle and must not trigger the
+// device-wide synchronisation cudaMalloc / cudaFree imply in the middle of a
+// step.  For them the packer's scratch lives in this library's image: one
+// 1 MiB array per GPU that loads the library, held until the process exits.
+//
+// Limits: T <= 8192 tokens and n_adapters <= 1024 per call (larger batches are
+// refused with VLR_ERR_STATIC_LIMIT; use vlr_pack with a caller workspace).
+// The array is shared by every call on the device and keeps the previous
+// call's bytes.  Nothing in it has to start at zero: the histogram rows are
+// written in full before they are read, every other array is written before it
+// is read within the call.  Two calls whose kernels overlap on the GPU (two
+// streams, two threads) race on the array; serialise them on one stream.
+// The first call on each device looks the array's device address up
+// (cudaGetSymbolAddress) and caches it; make that first call before any
+// stream capture begins.  No cudaMalloc, cudaFree or other allocating call
+// is made here.
+namespace vlr {
+
+constexpr int64_t kStaticMaxTokens = 8192;
+constexpr int64_t kStaticMaxAdapters = 1024;
+constexpr size_t kStaticScratchBytes = 1u << 20;
+
+static __device__ __align__(256) unsigned char g_pack_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_scratch_mu;
+static unsigned char* g_scratch_ptr[kMaxDevices];   // device address of g_pack_scratch, per device
+
+// In host code `g_pack_scratch` is only a handle for the runtime, not a device
+// address: the address is asked for once per device, with that device current.
+static int static_scratch(unsigned char** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return VLR_ERR_RANGE;
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_pack_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (p == nullptr) return VLR_ERR_DRIVER;
+    g_scratch_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_scratch_ptr[dev];
+  return VLR_OK;
+}
+
+}  // namespace vlr
+
+extern "C" int vlr_pack_static(const int64_t* tok_adapter, int64_t T, const int64_t* a_len,
+                               int64_t n_adapters, int sort, int tile_m, int mma_min_rows,
+                               int gather_rows_per_tile, int32_t* perm, int64_t* seg_len,
+                               int64_t* seg_rank, int64_t* seg_adapter, int64_t* seg_start,
+                               int32_t* tiles, int64_t tiles_cap, int32_t* gather_rows,
+                               int32_t* counts, void* stream) {
+  using namespace vlr;
+  if (!a_len || !perm || !seg_len || !seg_rank || !seg_adapter || !seg_start || !tiles ||
+      !gather_rows || !counts)
+    return VLR_ERR_NULL;
+  if (T > 0 && !tok_adapter) return VLR_ERR_NULL;
+  if (T < 0 || n_adapters <= 0 || tiles_cap < 0) return VLR_ERR_RANGE;
+  if (tile_m <= 0 || mma_min_rows <= 0 || gather_rows_per_tile <= 0) return VLR_ERR_RANGE;
+  if (T > kStaticMaxTokens || n_adapters > kStaticMaxAdapters) return VLR_ERR_STATIC_LIMIT;
+  unsigned char* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc != VLR_OK) return rc;
+  PackWs ws;
+  const size_t need = pack_ws_layout(T, n_adapters, &ws, reinterpret_cast<char*>(scratch));
+  if (need > kStaticScratchBytes) return VLR_ERR_STATIC_LIMIT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int nblk = (int)((T + kPackBlock - 1) / kPackBlock);
+  pack_clear_counts<<<1, 32, 0, s>>>(counts);
+  if (sort && T > 0) {
+    pack_hist_kernel<<<nblk, kPackBlock, n_adapters * sizeof(int32_t), s>>>(
+        tok_adapter, (int)T, (int)n_adapters, ws.hist, counts);
+    pack_scan_kernel<<<1, kScanThreads, 0, s>>>(nblk, (int)n_adapters, ws.hist, ws.abase);
+    pack_scatter_kernel<<<nblk, kPackBlock, 0, s>>>(tok_adapter, (int)T, (int)n_adapters, ws.hist,
+                                                    ws.abase, perm, ws.key, counts);
+  }
+  PackOut out{perm, seg_len, seg_rank, seg_adapter, seg_start, tiles, tiles_cap, gather_rows, counts};
+  pack_tiles_kernel<<<1, kScanThreads, 0, s>>>(tok_adapter, a_len, (int)T, (int)n_adapters,
+                                               sort && T > 0, tile_m, mma_min_rows,
+                                               gather_rows_per_tile, ws, out);
+  return launch_status();
 }

@@ -199,6 +199,33 @@ class Packer:
                       self.tiles, self.gather_rows, self.counts, self.workspace)
 
 
+def pack_static(packer: "Packer", tok_adapter: torch.Tensor, a_len: torch.Tensor,
+                sort: bool = True) -> Packed:
+    """Pack through vlr_pack_static: same outputs as packer.pack(), written into the
+    packer's output buffers, but the scratch is the library's built-in array, so
+    nothing here or in the library allocates.  For callers that cannot allocate
+    (all free HBM already claimed by the serving pool; FFI callers without an
+    allocator).  At most 8192 tokens and 1024 adapters; calls must not overlap
+    on the GPU; make the first call on a device outside stream capture."""
+    _check_input(tok_adapter, "tok_adapter")
+    _check_input(a_len, "a_len")
+    _i64(tok_adapter, "tok_adapter")
+    _i64(a_len, "a_len")
+    T = tok_adapter.numel()
+    if T > packer.max_tokens or a_len.numel() != packer.n_adapters:
+        raise RuntimeError("batch exceeds the packer's output capacity")
+    rc = packer.lib.vlr_pack_static(_ptr(tok_adapter), T, _ptr(a_len), packer.n_adapters,
+                                    int(bool(sort)), packer.tile_m, packer.mma_min_rows, packer.grp,
+                                    _ptr(packer.perm), _ptr(packer.seg_len), _ptr(packer.seg_rank),
+                                    _ptr(packer.seg_adapter), _ptr(packer.seg_start),
+                                    _ptr(packer.tiles), packer.tiles.size(0),
+                                    _ptr(packer.gather_rows), _ptr(packer.counts),
+                                    _stream(packer.device))
+    _lib.check(rc, "vlr_pack_static")
+    return Packed(T, packer.perm, packer.seg_len, packer.seg_rank, packer.seg_adapter,
+                  packer.seg_start, packer.tiles, packer.gather_rows, packer.counts, None)
+
+
 def var_len_copy(old_a_start, old_a_len, old_a_location, new_a_start, new_a_location):
     """Index-table compaction; arguments of launch_var_len_copy_triton
     (valora/server/router/model_infer/infer_adapter.py:277-282)."""
