@@ -120,19 +120,27 @@ def measured_peak():
         return 6650.0, "fallback (earlier measurement on this pool)"
 
 
-def phase_bytes(batch, tiles, n_mma, n_gather):
-    """Algorithmic HBM bytes of each of the four kernels for one step: the rows a
-    kernel covers (X once for a shrink; Y0 read + Y write for an expand) plus each
-    adapter's weights it touches, once.  2-byte elements; V and metadata excluded."""
+def phase_bytes(batch, tiles, n_mma, n_gather, merged):
+    """Algorithmic HBM bytes of each kernel launch of one step: the rows a kernel
+    covers (X once for a shrink; Y0 read + Y write for an expand) plus the weights
+    of every adapter it touches, once.  2-byte elements; V and metadata excluded.
+    merged: one shrink and one expand launch cover both kinds of tile."""
     mma, gat = tiles[:n_mma], tiles[n_mma:n_mma + n_gather]
     rows = {"mma": int(mma[:, 4].sum()) if n_mma else 0, "gather": int(gat[:, 4].sum()) if n_gather else 0}
-    rk = {"mma": int(batch.ranks[np.unique(mma[:, 1])].sum()) if n_mma else 0,
-          "gather": int(batch.ranks[np.unique(gat[:, 1])].sum()) if n_gather else 0}
+    ads = {"mma": np.unique(mma[:, 1]) if n_mma else np.zeros(0, np.int64),
+           "gather": np.unique(gat[:, 1]) if n_gather else np.zeros(0, np.int64)}
     out = {}
-    for kind in ("mma", "gather"):
-        sh = sum(rows[kind] * hi + rk[kind] * hi for _, hi, _ in batch.projections) * 2 * batch.layers
-        ex = sum(2 * rows[kind] * ho + rk[kind] * ho for _, _, ho in batch.projections) * 2 * batch.layers
-        out["shrink_" + kind], out["expand_" + kind] = sh, ex
+
+    def add(name_s, name_e, nrows, adapters):
+        rk = int(batch.ranks[adapters].sum()) if len(adapters) else 0
+        out[name_s] = sum(nrows * hi + rk * hi for _, hi, _ in batch.projections) * 2 * batch.layers
+        out[name_e] = sum(2 * nrows * ho + rk * ho for _, _, ho in batch.projections) * 2 * batch.layers
+
+    if merged:
+        add("shrink", "expand", rows["mma"] + rows["gather"], np.union1d(ads["mma"], ads["gather"]).astype(np.int64))
+    else:
+        for kind in ("mma", "gather"):
+            add("shrink_" + kind, "expand_" + kind, rows[kind], ads[kind].astype(np.int64))
     return out, rows
 
 
@@ -197,6 +205,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=LAYERS, help="for profiling small cases only")
+    ap.add_argument("--gather-path", default="mma", choices=["mma", "simt"],
+                    help="decode rows on the tensor-core kernels (gathered rows) or on the SIMT gather kernels")
     args = ap.parse_args()
 
     rank, world, local = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
@@ -221,7 +231,7 @@ def main():
     T = batch.T
     warmup = max(args.warmup, 3)
     eng = LoraStepEngine(batch.projections, batch.ranks, batch.scalings(), batch.dtype, dev,
-                         args.layers, T)
+                         args.layers, T, gather_path=args.gather_path)
     eng.randomize_weights(seed=batch.seed)
     g = torch.Generator(device=dev)
     g.manual_seed(batch.seed)
@@ -244,11 +254,14 @@ def main():
         raise SystemExit("a bounded wait gave up inside a kernel during warm-up")
     counts = packed.host_counts()
     tiles_h = packed.tiles.cpu().numpy()
-    pbytes, rows = phase_bytes(batch, tiles_h, counts["n_mma"], counts["n_gather"])
+    pbytes, rows = phase_bytes(batch, tiles_h, counts["n_mma"], counts["n_gather"],
+                               merged=args.gather_path == "mma")
+    kernel_names = [n for n, _ in eng.phases()]
+    n_ev = 2 + len(kernel_names)
 
     # ---- timed region: K steps, events between the stages of every step
     K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(K)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n_ev)] for _ in range(K)]
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.25)
@@ -260,8 +273,8 @@ def main():
     t1 = time.time()
     barrier()
     clocks = sampler.stop(t0, t1)
-    total_ms = ev[0][0].elapsed_time(ev[K - 1][5])
-    names = ["pack", "shrink_mma", "shrink_gather", "expand_mma", "expand_gather"]
+    total_ms = ev[0][0].elapsed_time(ev[K - 1][n_ev - 1])
+    names = ["pack"] + kernel_names
     phase_ms = {n: float(np.mean([ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K)]))
                 for i, n in enumerate(names)}
     if ops.device_status() != 0:
@@ -309,7 +322,7 @@ def main():
         return
 
     peak, peak_src = measured_peak()
-    dom = max(("shrink_mma", "shrink_gather", "expand_mma", "expand_gather"), key=lambda n: phase_ms[n])
+    dom = max(kernel_names, key=lambda n: phase_ms[n])
     achieved = pbytes[dom] / (phase_ms[dom] * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
@@ -325,7 +338,7 @@ def main():
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": batch.name, "tokens_per_gpu": T, "layers": args.layers,
                    "projections": len(batch.projections), "adapters_per_gpu": batch.n_adapters, "rank": 64,
-                   "parallelism": f"adapter-group x{world}", "mma_tiles": counts["n_mma"],
+                   "parallelism": f"adapter-group x{world}", "gather_path": args.gather_path, "mma_tiles": counts["n_mma"],
                    "gather_tiles": counts["n_gather"], "rows_mma": rows["mma"], "rows_gather": rows["gather"],
                    "l2": "inputs larger than L2 (every step streams tens of GB of distinct buffers)",
                    "algorithmic_bytes_per_step": step_bytes,
@@ -335,7 +348,7 @@ def main():
                    "phase_ms": phase_ms, "phase_algorithmic_bytes": pbytes},
         "clocks": clocks,
         "e2e": e2e,
-        "gpu_launches": 9 * K,
+        "gpu_launches": (5 + len(kernel_names)) * K,
         "roofline": {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": pbytes[dom], "ms_per_launch": phase_ms[dom]},

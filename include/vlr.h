@@ -168,6 +168,12 @@ int vlr_pack_static(const int64_t* tok_adapter, int64_t T, const int64_t* a_len,
 int vlr_var_len_copy(const int64_t* old_start, const int64_t* len, const int64_t* old_loc,
                      const int64_t* new_start, int64_t* new_loc, int64_t n, void* stream);
 
+/* Debug aid.  While a device buffer of n_int64 int64 is set, CTA 0 of the
+ * tensor-core kernels stamps clock64 into it, 8 values per pipeline stage
+ * (0 stage issued, 1 operands seen by the MMA thread, 2 MMAs issued or epilogue
+ * started, 3 stage released, 4-7 points inside the epilogue).  NULL switches it off. */
+int vlr_debug_set_trace(void* dev_buffer, int64_t n_int64);
+
 /* Bind the calling thread's CUDA runtime state to a device (cudaSetDevice). */
 int vlr_set_device(int device);
 
@@ -178,9 +184,9 @@ int vlr_device_status(int reset);
 
 /*
  * One step over many projections: shrink then expand of every (layer, projection)
- * problem of a packed batch, enqueued as four batched launches (tensor-core
- * shrink, gather shrink, tensor-core expand, gather expand) that cover all
- * problems at once.  No counterpart in the reference, which issues 6-8 calls per
+ * problem of a packed batch, enqueued as batched launches that cover all problems
+ * at once: tensor-core shrink and expand, plus (unless
+ * VLR_STEP_GATHER_ON_TENSOR_CORES is set) a SIMT gather shrink and expand.  No counterpart in the reference, which issues 6-8 calls per
  * layer from Python with a host synchronisation after each
  * (valora/models/peft/lora_unordered_batch_infer.py:946-988).
  *
@@ -231,6 +237,12 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
 #define VLR_PHASE_EXPAND_MMA 4
 #define VLR_PHASE_EXPAND_GATHER 8
 #define VLR_PHASE_ALL 15
+/* or-ed into phase_mask: the gather tiles (rows that are not consecutive in the
+ * batch, e.g. decode tokens) are processed by the two tensor-core launches, their
+ * rows fetched with 128-byte 1-D bulk copies instead of tiled bulk copies; the
+ * two SIMT gather launches are skipped.  gather_rows_per_tile must be <= 16 with
+ * this flag and <= 8 without it.  Plans need h_in and h_out multiples of 64. */
+#define VLR_STEP_GATHER_ON_TENSOR_CORES 16
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
                   const int32_t* counts, const void* scales, int max_h_in, int max_h_out,

@@ -329,11 +329,11 @@ def test_dropin_modules(ops):
 
 
 # --------------------------------------------------------------------------- step (packed batch, many problems)
-def _step_case(ops, batch, proj_ids, layers=1, mma_min=16):
+def _step_case(ops, batch, proj_ids, layers=1, mma_min=16, gather_path="mma"):
     from valora_b200.engine import LoraStepEngine
     projs = [batch.projections[p] for p in proj_ids]
     eng = LoraStepEngine(projs, batch.ranks, batch.scalings(), batch.dtype, DEV, layers, batch.T,
-                         mma_min_rows=mma_min)
+                         mma_min_rows=mma_min, gather_path=gather_path)
     g = torch.Generator().manual_seed(batch.seed)
     W = {}
     for layer in range(layers):
@@ -371,14 +371,16 @@ def _step_case(ops, batch, proj_ids, layers=1, mma_min=16):
     return eng
 
 
-def test_step_config0(ops):
-    _step_case(ops, workloads.config0(), [0])
+@pytest.mark.parametrize("gather_path", ["mma", "simt"])
+def test_step_config0(ops, gather_path):
+    _step_case(ops, workloads.config0(), [0], gather_path=gather_path)
 
 
-def test_step_config3_mixed_two_widths(ops):
+@pytest.mark.parametrize("gather_path", ["mma", "simt"])
+def test_step_config3_mixed_two_widths(ops, gather_path):
     """mixed prefill + decode batch of config 3, one layer, q / up / down projections
-    (4096->4096, 4096->11008, 11008->4096): tensor-core tiles and gather tiles together"""
-    _step_case(ops, workloads.config3(layers=1), [0, 4, 6])
+    (4096->4096, 4096->11008, 11008->4096): consecutive-row tiles and gathered rows together"""
+    _step_case(ops, workloads.config3(layers=1), [0, 4, 6], gather_path=gather_path)
 
 
 def test_step_config2_hetero_ranks_two_layers(ops):
@@ -386,6 +388,14 @@ def test_step_config2_hetero_ranks_two_layers(ops):
     _step_case(ops, b, [0, 3], layers=2)
 
 
-def test_step_all_gather_rows(ops):
-    """decode-only batch (config 1): every row goes through the gather path"""
-    _step_case(ops, workloads.config1(), [0])
+@pytest.mark.parametrize("gather_path", ["mma", "simt"])
+def test_step_all_gather_rows(ops, gather_path):
+    """decode-only batch (config 1): every row is a gathered row"""
+    _step_case(ops, workloads.config1(), [0], gather_path=gather_path)
+
+
+def test_step_gathered_rows_mixed_ranks(ops):
+    """config 4 slice: 1024 adapters of ranks 16..128, mostly decode rows, many adapters
+    with a handful of rows each - gathered tiles of every rank on the tensor cores"""
+    b = workloads.config4(n_gpus=8, rank=3)
+    _step_case(ops, b, [0])

@@ -19,6 +19,7 @@ _SIGS = {
     "vlr_version": (c_int, []),
     "vlr_error_string": (ctypes.c_char_p, [c_int]),
     "vlr_set_device": (c_int, [c_int]),
+    "vlr_debug_set_trace": (c_int, [c_vp, c_i64]),
     "vlr_device_status": (c_int, [c_int]),
     "vlr_bgmv": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp,
                          c_i64, c_i64, c_i64, c_int, c_int, c_vp]),

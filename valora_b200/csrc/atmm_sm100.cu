@@ -30,10 +30,17 @@ namespace vlr {
 using namespace ptx;
 
 constexpr int kTileM = 128;
-constexpr int kThreads = 192;
-constexpr int kBoxRowsAct = 32;      // activation rows per TMA box
+// Warp roles.  Issuing a stage (barrier wait, expect_tx, two to four bulk copies)
+// costs one thread several hundred cycles, so stages are dealt round-robin to
+// several producer warps.  Epilogue warps start at a multiple of 4 so that
+// warp % 4 is the tensor-memory lane quarter a warp may read.
+constexpr int kShrinkProducers = 3;                    // warps 0..2, MMA = warp 3, epilogue = 4..7
+constexpr int kShrinkMmaWarp = kShrinkProducers;
+constexpr int kShrinkEpiWarp0 = 4;
+constexpr int kThreads = 32 * (kShrinkEpiWarp0 + 4);
 constexpr int kBoxRowsW = 16;        // weight rows per TMA box
 constexpr int kBoxCols = 64;         // 64 two-byte elements = 128 bytes = swizzle span
+constexpr int kGatherRows = 16;      // rows of a gather tile (row slots 0, 8, ..., 120)
 
 struct TileInfo {
   int valid;
@@ -43,8 +50,50 @@ struct TileInfo {
   int adapter;
   int problem;       // index into the step plan (0 outside step mode)
   int split;         // expand: which share of the output columns
+  int gather;        // 1: the rows are gather_rows[row0 .. row0+rows), not consecutive.
+                     //    Row i of such a tile (at most 16 rows) goes to lane quarter i % 4 of the
+                     //    128-row MMA tile, so that all four SM sub-partitions (each reads only its
+                     //    own quarter of tensor memory) share the epilogue:
+                     //    shrink: slot (i%4)*32 + (i/4)*8 - the first row of a swizzle atom, where
+                     //            the 128-byte swizzle is the identity, so a plain 128-byte bulk
+                     //            copy of the activation row lands in the right layout;
+                     //    expand: slot (i%4)*32 + i/4 (the V operand is written by generic stores).
   int64_t wrow0;     // first pool cell of the slot
 };
+
+// row r of a tile -> row of the caller's x / y / v
+__device__ __forceinline__ int tile_row(const TileSource& src, const TileInfo& ti, int r) {
+  return ti.gather ? src.gather_rows[ti.row0 + r] : ti.row0 + r;
+}
+
+// Consecutive activation rows [row0, row0 + rows) as one to two boxes (32 / 64 /
+// 128 rows): the copy covers rows rounded up to 32.  dst is the tile's first row.
+__device__ __forceinline__ int act_rows_loaded(int rows) { return (rows + 31) & ~31; }
+__device__ __forceinline__ void load_act_rows(uint32_t dst, const MapSet* ms, int c0, int row0,
+                                              int rows, uint32_t bar) {
+  const int n32 = (rows + 31) >> 5;                  // 1..4
+  if (n32 == 4) {
+    tma_load_2d(dst, &ms->act[2], c0, row0, bar);
+  } else if (n32 == 1) {
+    tma_load_2d(dst, &ms->act[0], c0, row0, bar);
+  } else {
+    tma_load_2d(dst, &ms->act[1], c0, row0, bar);
+    if (n32 == 3) tma_load_2d(dst + 64 * 128, &ms->act[0], c0, row0 + 64, bar);
+  }
+}
+// n_pad (multiple of 16, <= 128) consecutive pool cells as at most four boxes
+__device__ __forceinline__ void load_w_rows(uint32_t dst, const MapSet* ms, int c0, int row0,
+                                            int n_pad, uint32_t bar) {
+  int done = 0;
+#pragma unroll
+  for (int b = 3; b >= 0; --b) {
+    const int h = 16 << b;
+    if (n_pad - done >= h) {
+      tma_load_2d(dst + done * 128, &ms->w[b], c0, row0 + done, bar);
+      done += h;
+    }
+  }
+}
 
 // Item -> tile.  Warp-collective: all 32 lanes call it and all get the result.
 // mode 1: item = (problem * n_tiles + tile) * nsplit + split, n_tiles on the device.
@@ -55,14 +104,17 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
   TileInfo ti;
   ti.valid = 0;
   ti.problem = 0;
+  ti.gather = 0;
   ti.split = (int)(item % src.nsplit);
   const int64_t tb = item / src.nsplit;
   if (src.mode == 1) {
-    const int n_tiles = src.counts[VLR_COUNT_MMA_TILES];
+    const int n_tiles = src.counts[VLR_COUNT_MMA_TILES] +
+                        (src.gather_mma ? src.counts[VLR_COUNT_GATHER_TILES] : 0);
     const int b = (int)(tb % n_tiles);
     ti.problem = (int)(tb / n_tiles);
     const int32_t* t = src.tiles + (int64_t)b * VLR_TILE_INTS;
     ti.valid = 1;
+    ti.gather = t[0] == VLR_TILE_GATHER;
     ti.adapter = t[1];
     ti.rank = t[2];
     ti.row0 = t[3];
@@ -98,7 +150,8 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
     }
   }
   if (ti.valid) {
-    if (ti.rank <= 0 || ti.rank > kMaxRank || (ti.rank & 7) || ti.rows <= 0 || ti.rows > kTileM) {
+    if (ti.rank <= 0 || ti.rank > kMaxRank || (ti.rank & 7) || ti.rows <= 0 ||
+        ti.rows > (ti.gather ? kGatherRows : kTileM)) {
       ti.valid = 0;                  // host validated what it could; skip bad entries
     } else {
       const int64_t* a_start = src.a_start;
@@ -118,11 +171,19 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
 
 __device__ __forceinline__ int64_t total_items(const TileSource& src) {
   if (src.mode == 1)
-    return (int64_t)src.counts[VLR_COUNT_MMA_TILES] * src.n_problems * src.nsplit;
+    return (int64_t)(src.counts[VLR_COUNT_MMA_TILES] +
+                     (src.gather_mma ? src.counts[VLR_COUNT_GATHER_TILES] : 0)) *
+           src.n_problems * src.nsplit;
   return src.max_tiles * src.nsplit;
 }
 
 __device__ int g_status;             // 0 ok, 1 a bounded wait gave up
+
+// Debug aid: CTA 0 stamps clock64 into src.trace, slot `what` of stage `k`.
+__device__ __forceinline__ void trace_stamp(const TileSource& src, uint32_t k, int what) {
+  if (src.trace != nullptr && blockIdx.x == 0 && (int64_t)k * 8 + what < src.trace_cap)
+    src.trace[(int64_t)k * 8 + what] = clock64();
+}
 
 // ============================================================================
 // shrink: persistent CTAs, 6-stage TMA ring over K, two accumulators in tensor
@@ -136,8 +197,9 @@ constexpr int kShrinkSmem = 1024 + kShrinkStages * kShrinkStageBytes + 256;
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-atmm_shrink_kernel(const __grid_constant__ CUtensorMap map_x_, const __grid_constant__ CUtensorMap map_w_,
-                   T* __restrict__ v_, TileSource src, int h_in_, int v_pitch_, int accumulate) {
+atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
+                   T* __restrict__ v_, const T* __restrict__ x_, TileSource src, int h_in_,
+                   int v_pitch_, int accumulate) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_s;
   __shared__ uint32_t tmem_base_s;
@@ -167,55 +229,75 @@ atmm_shrink_kernel(const __grid_constant__ CUtensorMap map_x_, const __grid_cons
     }
     fence_barrier_init();
   }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), 256);
+  if (warp == kShrinkMmaWarp) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  // Tensor memory: two tile buffers of 256 columns.  A buffer holds 256 / n_pad'
+  // (n_pad' = 64 or 128) partial accumulators; the K slices of a stage go to them in
+  // turn, so consecutive MMAs do not wait on each other's accumulator, and the
+  // epilogue adds the partial sums.
+  auto acc_stride = [](int n_pad) { return n_pad <= 64 ? 64 : 128; };
 
   // per-item problem view
   auto h_in_of = [&](const TileInfo& ti) { return src.plan ? src.plan[ti.problem].h_in : h_in_; };
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp < kShrinkProducers) {
+    // ------------------------------------------------------------ producers (stage k -> warp k % 3)
+    // lane 0: TMA boxes (weights; consecutive activation rows).  Gather tiles: lane i
+    // copies row i, 128 bytes per K block, with a 1-D bulk copy into row slot 8*i.
     uint32_t kiter = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
       const TileInfo ti = get_tile(src, item, false);
       if (!ti.valid) continue;
-      if (lane == 0) {
-        const CUtensorMap* pmap_x = src.plan ? &src.plan[ti.problem].map_x : &map_x_;
-        const CUtensorMap* pmap_w = src.plan ? &src.plan[ti.problem].map_wa : &map_w_;
-        const int n_pad = (ti.rank + 15) & ~15;
-        const int nbox_x = (ti.rows + kBoxRowsAct - 1) / kBoxRowsAct;
-        const int nbox_w = n_pad / kBoxRowsW;
-        const int kblocks = (h_in_of(ti) + kBoxCols - 1) / kBoxCols;
-        const uint32_t bytes = (uint32_t)(nbox_x * kBoxRowsAct + nbox_w * kBoxRowsW) * 128u;
-        for (int kb = 0; kb < kblocks; ++kb, ++kiter) {
-          const int s = kiter % kShrinkStages;
-          if (!mbar_wait(empty_bar(s), ((kiter / kShrinkStages) & 1) ^ 1, &abort_s)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), bytes);
-          for (int i = 0; i < nbox_x; ++i)
-            tma_load_2d(x_stage(s) + i * (kBoxRowsAct * 128), pmap_x, kb * kBoxCols,
-                        ti.row0 + i * kBoxRowsAct, full_bar(s));
-          for (int i = 0; i < nbox_w; ++i)
-            tma_load_2d(w_stage(s) + i * (kBoxRowsW * 128), pmap_w, kb * kBoxCols,
-                        (int)ti.wrow0 + i * kBoxRowsW, full_bar(s));
+      const MapSet* ms = src.plan ? &src.plan[ti.problem].shrink : &maps_;
+      const T* xg = src.plan ? reinterpret_cast<const T*>(src.plan[ti.problem].x) : x_;
+      const int h_in = h_in_of(ti);
+      const int n_pad = (ti.rank + 15) & ~15;
+      const int kblocks = (h_in + kBoxCols - 1) / kBoxCols;
+      const bool mine = ti.gather && lane < ti.rows;
+      const T* xrow = mine ? xg + (int64_t)src.gather_rows[ti.row0 + lane] * h_in : xg;
+      if (lane < 7) prefetch_tensormap(lane < 3 ? &ms->act[lane] : &ms->w[lane - 3]);
+      const uint32_t bytes =
+          (uint32_t)((ti.gather ? ti.rows : act_rows_loaded(ti.rows)) + n_pad) * 128u;
+      for (int kb = 0; kb < kblocks; ++kb, ++kiter) {
+        if ((int)(kiter % kShrinkProducers) != warp) continue;   // another producer's stage
+        const int s = kiter % kShrinkStages;
+        if (lane == 0) {
+          ok = mbar_wait(empty_bar(s), ((kiter / kShrinkStages) & 1) ^ 1, &abort_s);
+          if (ok) {
+            trace_stamp(src, kiter, 0);
+            mbar_expect_tx(full_bar(s), bytes);
+            if (!ti.gather) load_act_rows(x_stage(s), ms, kb * kBoxCols, ti.row0, ti.rows, full_bar(s));
+            load_w_rows(w_stage(s), ms, kb * kBoxCols, (int)ti.wrow0, n_pad, full_bar(s));
+            trace_stamp(src, kiter, 3);
+          }
+        }
+        if (lane == 0 && !ok && !ti.gather) break;
+        if (ti.gather) {
+          ok = __shfl_sync(0xffffffffu, ok, 0);        // also orders expect_tx before the copies
+          if (!ok) break;
+          if (mine)
+            bulk_load_1d(x_stage(s) + ((lane & 3) * 32 + (lane >> 2) * 8) * 128, xrow + kb * kBoxCols,
+                         128, full_bar(s));
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
     }
-    if (lane == 0 && abort_s) {
+    __syncwarp();
+    if (warp == 0 && lane == 0 && abort_s) {
       // drain: let every copy that was issued land before the CTA retires
       volatile int none = 0;
       const uint32_t first = kiter > (uint32_t)kShrinkStages ? kiter - kShrinkStages : 0;
       for (uint32_t k = first; k < kiter; ++k)
         mbar_wait(full_bar(k % kShrinkStages), (k / kShrinkStages) & 1, &none);
     }
-  } else if (warp == 1) {
+  } else if (warp == kShrinkMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
     uint32_t kiter = 0, li = 0;
     bool ok = true;
@@ -227,21 +309,24 @@ atmm_shrink_kernel(const __grid_constant__ CUtensorMap map_x_, const __grid_cons
         const int kblocks = (h_in_of(ti) + kBoxCols - 1) / kBoxCols;
         const uint32_t idesc = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, n_pad, 0);
         const int ab = li & 1;
-        const uint32_t tacc = tmem_base + ab * kMaxRank;
+        const uint32_t tacc = tmem_base + ab * 256;
+        const int astr = acc_stride(n_pad), nacc = 256 / astr;
         ok = mbar_wait(tempty_bar(ab), ((li >> 1) & 1) ^ 1, &abort_s);
         if (ok) tc_fence_after();
         for (int kb = 0; kb < kblocks && ok; ++kb, ++kiter) {
           const int s = kiter % kShrinkStages;
           ok = mbar_wait(full_bar(s), (kiter / kShrinkStages) & 1, &abort_s);
           if (!ok) break;
+          trace_stamp(src, kiter, 1);
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < kBoxCols / 16; ++k) {
             const uint64_t ad = smem_desc_sw128(x_stage(s) + k * 32, 16, 1024);
             const uint64_t bd = smem_desc_sw128(w_stage(s) + k * 32, 16, 1024);
-            umma_f16(tacc, ad, bd, idesc, (kb | k) != 0);
+            umma_f16(tacc + (k % nacc) * astr, ad, bd, idesc, (kb * (kBoxCols / 16) + k) >= nacc);
           }
           umma_commit(empty_bar(s));
+          trace_stamp(src, kiter, 2);
         }
         if (ok) umma_commit(tfull_bar(ab));
         ++li;
@@ -266,13 +351,24 @@ atmm_shrink_kernel(const __grid_constant__ CUtensorMap map_x_, const __grid_cons
         v_pitch = kMaxRank;
       }
       const int n_pad = (ti.rank + 15) & ~15;
-      if (q * 32 < ti.rows) {
-        T* vrow = v + (int64_t)(ti.row0 + row) * v_pitch;
+      // tile row held by this lane: slot = row for consecutive rows, slot 8*i for gathered row i
+      const int trow = ti.gather ? (((lane & 7) == 0 && lane < 32) ? (lane >> 3) * 4 + q : kTileM) : row;
+      const bool warp_live = ti.gather ? q < ti.rows : q * 32 < ti.rows;
+      if (warp_live) {
+        T* vrow = v + (int64_t)(trow < ti.rows ? tile_row(src, ti, trow) : 0) * v_pitch;
+        const int astr = acc_stride(n_pad), nacc = 256 / astr;
         for (int c = 0; c < n_pad; c += 16) {
           uint32_t r[16];
-          tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + ab * kMaxRank + c, r);
+          tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + c, r);
+          for (int a = 1; a < nacc; ++a) {
+            uint32_t p[16];
+            tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + a * astr + c, p);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(p[e]));
+          }
           tmem_ld_wait();
-          if (row < ti.rows) {
+          if (trow < ti.rows) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int col = c + h * 8;
@@ -300,9 +396,9 @@ atmm_shrink_kernel(const __grid_constant__ CUtensorMap map_x_, const __grid_cons
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kShrinkMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && abort_s) g_status = 1;
 }
@@ -312,6 +408,12 @@ atmm_shrink_kernel(const __grid_constant__ CUtensorMap map_x_, const __grid_cons
 // then a 3-stage ring streams (B tile, Y tile) pairs, 128 output columns each.
 // ============================================================================
 constexpr int kExpStages = 3;
+constexpr int kExpEpiWarps = 16;                       // 4 per TMEM lane quarter, 32 columns each
+constexpr int kExpEpiWarp0 = 0;                        // epilogue = warps 0..15
+constexpr int kExpProducers = 2;                       // producers = warps 16..17
+constexpr int kExpProdWarp0 = kExpEpiWarps;
+constexpr int kExpMmaWarp = kExpProdWarp0 + kExpProducers;   // warp 18
+constexpr int kExpThreads = 32 * (kExpMmaWarp + 1);
 constexpr int kExpTileN = 128;
 constexpr int kExpABytes = 2 * kTileM * 128;           // V tile, two 64-column K blocks: 32 KB
 constexpr int kExpBBytes = 2 * kMaxRank * 128;         // two 64-column N blocks x 128 rows: 32 KB
@@ -319,12 +421,19 @@ constexpr int kExpYBytes = 2 * kTileM * 128;           // two 64-column blocks x
 constexpr int kExpStageBytes = kExpBBytes + kExpYBytes;
 constexpr int kExpSmem = 1024 + kExpABytes + kExpStages * kExpStageBytes + 256;
 
-struct ExpRange { int nt_begin, nt_count, h_out; };
+// A work item's output tiles.  Consecutive-row tiles use 128 columns per stage
+// (B 64-column blocks 16 KB apart).  Gather tiles stream almost only weights, so
+// with rank <= 64 they take 256 columns per stage (blocks 8 KB apart): twice the
+// bytes in flight per stage.
+struct ExpRange { int nt_begin, nt_count, h_out, ncbt, tile_n; uint32_t bstride; };
 
 __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileInfo& ti, int h_out_) {
   ExpRange r;
   r.h_out = src.plan ? src.plan[ti.problem].h_out : h_out_;
-  const int ntiles = (r.h_out + kExpTileN - 1) / kExpTileN;
+  r.ncbt = (ti.gather && ti.rank <= 64) ? 4 : 2;
+  r.tile_n = r.ncbt * kBoxCols;
+  r.bstride = (uint32_t)(kExpBBytes / r.ncbt);
+  const int ntiles = (r.h_out + r.tile_n - 1) / r.tile_n;
   const int per = (ntiles + src.nsplit - 1) / src.nsplit;
   r.nt_begin = ti.split * per;
   r.nt_count = max(0, min(per, ntiles - r.nt_begin));
@@ -332,8 +441,8 @@ __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileI
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
-atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_constant__ CUtensorMap map_w_,
+__global__ void __launch_bounds__(kExpThreads, 1)
+atmm_expand_kernel(const __grid_constant__ MapSet maps_,
                    T* __restrict__ y_, const T* __restrict__ v_, const T* __restrict__ scales,
                    TileSource src, int h_out_, int v_pitch_, int apply_scale) {
   extern __shared__ uint8_t smem_raw[];
@@ -360,18 +469,18 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
     abort_s = 0;
     for (int s = 0; s < kExpStages; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 4);
+      mbar_init(empty_bar(s), kExpEpiWarps);
     }
     for (int ab = 0; ab < 2; ++ab) {
       mbar_init(tfull_bar(ab), 1);
-      mbar_init(tempty_bar(ab), 4);
+      mbar_init(tempty_bar(ab), kExpEpiWarps);
     }
-    mbar_init(a_ready_bar, 128);
+    mbar_init(a_ready_bar, 32 * kExpEpiWarps);
     mbar_init(a_free_bar, 1);
     fence_barrier_init();
   }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), 256);
+  if (warp == kExpMmaWarp) {
+    tmem_alloc(smem_u32(&tmem_base_s), 512);           // two accumulators of up to 256 columns
     tmem_relinquish();
   }
   tc_fence_before();
@@ -379,48 +488,66 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp >= kExpProdWarp0 && warp < kExpMmaWarp) {
+    // ------------------------------------------------------------ producers (stage k -> warp k % 2)
+    const int pw = warp - kExpProdWarp0;
+    // lane 0: TMA boxes (B rows; consecutive Y rows).  Gather tiles: lane i copies the
+    // 128-byte pieces of Y row i with 1-D bulk copies, packed 16 rows x 128 bytes per
+    // 64-column block (read back by the epilogue only, so no swizzle).
     uint32_t it = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
       const TileInfo ti = get_tile(src, item, true);
       if (!ti.valid) continue;
       const ExpRange er = exp_range(src, ti, h_out_);
-      if (lane == 0) {
-        const CUtensorMap* pmap_y = src.plan ? &src.plan[ti.problem].map_y : &map_y_;
-        const CUtensorMap* pmap_w = src.plan ? &src.plan[ti.problem].map_wb : &map_w_;
-        const int k_pad = (ti.rank + 15) & ~15;
-        const int ksteps = k_pad / 16;
-        const int nbox_y = (ti.rows + kBoxRowsAct - 1) / kBoxRowsAct;
-        for (int t = 0; t < er.nt_count; ++t, ++it) {
-          const int s = it % kExpStages;
-          if (!mbar_wait(empty_bar(s), ((it / kExpStages) & 1) ^ 1, &abort_s)) { ok = false; break; }
-          const int n0 = (er.nt_begin + t) * kExpTileN;
-          const int ncb = min(2, (er.h_out - n0 + kBoxCols - 1) / kBoxCols);
-          const uint32_t bytes = (uint32_t)ncb * (uint32_t)(k_pad + nbox_y * kBoxRowsAct) * 128u;
-          mbar_expect_tx(full_bar(s), bytes);
-          for (int cb = 0; cb < ncb; ++cb)
-            for (int j = 0; j < ksteps; ++j)
-              tma_load_2d(b_stage(s) + cb * (kMaxRank * 128) + j * (kBoxRowsW * 128), pmap_w,
-                          n0 + cb * kBoxCols, (int)ti.wrow0 + j * kBoxRowsW, full_bar(s));
-          for (int cb = 0; cb < ncb; ++cb)
-            for (int i = 0; i < nbox_y; ++i)
-              tma_load_2d(y_stage(s) + cb * (kTileM * 128) + i * (kBoxRowsAct * 128), pmap_y,
-                          n0 + cb * kBoxCols, ti.row0 + i * kBoxRowsAct, full_bar(s));
+      const MapSet* ms = src.plan ? &src.plan[ti.problem].expand : &maps_;
+      const T* yg = src.plan ? reinterpret_cast<const T*>(src.plan[ti.problem].y) : y_;
+      const int k_pad = (ti.rank + 15) & ~15;
+      const int y_rows = ti.gather ? ti.rows : act_rows_loaded(ti.rows);
+      const bool mine = ti.gather && lane < ti.rows;
+      const T* yrow = mine ? yg + (int64_t)src.gather_rows[ti.row0 + lane] * er.h_out : yg;
+      if (lane < 7) prefetch_tensormap(lane < 3 ? &ms->act[lane] : &ms->w[lane - 3]);
+      for (int t = 0; t < er.nt_count; ++t, ++it) {
+        if ((int)(it % kExpProducers) != pw) continue;            // the other producer's stage
+        const int s = it % kExpStages;
+        const int n0 = (er.nt_begin + t) * er.tile_n;
+        const int ncb = min(er.ncbt, (er.h_out - n0 + kBoxCols - 1) / kBoxCols);
+        if (lane == 0) {
+          ok = mbar_wait(empty_bar(s), ((it / kExpStages) & 1) ^ 1, &abort_s);
+          if (ok) {
+            trace_stamp(src, it, 0);
+            const uint32_t bytes = (uint32_t)ncb * (uint32_t)(k_pad + y_rows) * 128u;
+            mbar_expect_tx(full_bar(s), bytes);
+            for (int cb = 0; cb < ncb; ++cb)
+              load_w_rows(b_stage(s) + cb * er.bstride, ms, n0 + cb * kBoxCols, (int)ti.wrow0,
+                          k_pad, full_bar(s));
+            if (!ti.gather)
+              for (int cb = 0; cb < ncb; ++cb)
+                load_act_rows(y_stage(s) + cb * (kTileM * 128), ms, n0 + cb * kBoxCols, ti.row0,
+                              ti.rows, full_bar(s));
+          }
+        }
+        if (lane == 0 && !ok && !ti.gather) break;
+        if (ti.gather) {
+          ok = __shfl_sync(0xffffffffu, ok, 0);        // also orders expect_tx before the copies
+          if (!ok) break;
+          if (mine)
+            for (int cb = 0; cb < ncb; ++cb)
+              bulk_load_1d(y_stage(s) + cb * (kGatherRows * 128) + lane * 128,
+                           yrow + n0 + cb * kBoxCols, 128, full_bar(s));
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
     }
-    if (lane == 0 && abort_s) {
+    __syncwarp();
+    if (pw == 0 && lane == 0 && abort_s) {
       volatile int none = 0;
       const uint32_t first = it > (uint32_t)kExpStages ? it - kExpStages : 0;
       for (uint32_t k = first; k < it; ++k)
         mbar_wait(full_bar(k % kExpStages), (k / kExpStages) & 1, &none);
     }
-  } else if (warp == 1) {
+  } else if (warp == kExpMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, kExpTileN, 1);
     uint32_t it = 0, li = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
@@ -430,6 +557,7 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
       if (er.nt_count <= 0) continue;
       const int k_pad = (ti.rank + 15) & ~15;
       const int ksteps = k_pad / 16;
+      const uint32_t idesc = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, er.tile_n, 1);
       ok = __all_sync(0xffffffffu, mbar_wait(a_ready_bar, li & 1, &abort_s));
       for (int t = 0; t < er.nt_count && ok; ++t, ++it) {
         const int s = it % kExpStages, ab = it & 1;
@@ -441,9 +569,9 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
           // rank % 16 == 8: rows rank..k_pad-1 of the B tile belong to the next slot.
           // The matching V columns are zero, but 0 * Inf/NaN would poison the sum.
           const int nrow = k_pad - ti.rank;            // 8
-          for (int i = lane; i < 2 * nrow * 8; i += 32) {
+          for (int i = lane; i < er.ncbt * nrow * 8; i += 32) {
             const int cb = i / (nrow * 8), rr = (i / 8) % nrow, ch = i % 8;
-            sts128(b_stage(s) + cb * (kMaxRank * 128) + (ti.rank + rr) * 128 + ch * 16,
+            sts128(b_stage(s) + cb * er.bstride + (ti.rank + rr) * 128 + ch * 16,
                    make_uint4(0, 0, 0, 0));
           }
           fence_proxy_async_smem();
@@ -451,10 +579,11 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
         }
         tc_fence_after();
         if (lane == 0) {
+          trace_stamp(src, it, 1);
           for (int j = 0; j < ksteps; ++j) {
             const uint64_t ad = smem_desc_sw128(a_tile + (j >> 2) * (kTileM * 128) + (j & 3) * 32, 16, 1024);
-            const uint64_t bd = smem_desc_sw128(b_stage(s) + j * (kBoxRowsW * 128), kMaxRank * 128, 1024);
-            umma_f16(tmem_base + ab * kExpTileN, ad, bd, idesc, j != 0);
+            const uint64_t bd = smem_desc_sw128(b_stage(s) + j * (kBoxRowsW * 128), er.bstride, 1024);
+            umma_f16(tmem_base + ab * 256, ad, bd, idesc, j != 0);
           }
           umma_commit(tfull_bar(ab));
         }
@@ -464,10 +593,14 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
       __syncwarp();
       ++li;
     }
-  } else {
+  } else if (warp < kExpEpiWarps) {
     // ------------------------------------------------------------ V staging + epilogue
-    const int q = warp & 3;
+    // 16 warps: warp (q, j) owns TMEM lanes 32q..32q+31 (rows) and columns 32j..32j+31
+    // of every 128-column output tile.
+    const int q = warp & 3;                            // the lane quarter a warp may read
+    const int j = (warp - kExpEpiWarp0) >> 2;                     // its 32-column slice
     const int row = q * 32 + lane;
+    const int et = threadIdx.x - 32 * kExpEpiWarp0;    // 0..511
     uint32_t it = 0, li = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
@@ -485,16 +618,21 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
       }
       const int h_out = er.h_out;
       const int k_pad = (ti.rank + 15) & ~15;
-      const bool warp_live = q * 32 < ti.rows;
+      // tile row held by this lane (gathered row i sits in slot (i%4)*32 + i/4)
+      const int trow = ti.gather ? (lane < 4 ? lane * 4 + q : kTileM) : row;
+      const bool warp_live = ti.gather ? q < ti.rows : q * 32 < ti.rows;
+      T* yout = y + (int64_t)(trow < ti.rows ? tile_row(src, ti, trow) : 0) * h_out;
       // ---- stage V as the K-major, 128-byte-swizzled A operand (zeros beyond rank / rows)
       ok = __all_sync(0xffffffffu, mbar_wait(a_free_bar, (li & 1) ^ 1, &abort_s));
       if (!ok) break;
       {
-        const T* vrow = v + (int64_t)(ti.row0 + row) * v_pitch;
-        for (int c8 = 0; c8 < k_pad / 8; ++c8) {
+        const int vr = et & 127;                       // row slot
+        const int vt = ti.gather ? ((vr & 31) < 4 ? (vr & 31) * 4 + (vr >> 5) : kTileM) : vr;
+        const T* vrow = v + (int64_t)(vt < ti.rows ? tile_row(src, ti, vt) : 0) * v_pitch;
+        for (int c8 = et >> 7; c8 < k_pad / 8; c8 += 4) {
           uint4 val = make_uint4(0, 0, 0, 0);
-          if (row < ti.rows && c8 * 8 < ti.rank) val = ldg128(vrow + c8 * 8);
-          sts128(a_tile + (c8 >> 3) * (kTileM * 128) + row * 128 + (((c8 & 7) ^ (row & 7)) << 4), val);
+          if (vt < ti.rows && c8 * 8 < ti.rank) val = ldg128(vrow + c8 * 8);
+          sts128(a_tile + (c8 >> 3) * (kTileM * 128) + vr * 128 + (((c8 & 7) ^ (vr & 7)) << 4), val);
         }
         fence_proxy_async_smem();
         mbar_arrive(a_ready_bar);
@@ -507,57 +645,96 @@ atmm_expand_kernel(const __grid_constant__ CUtensorMap map_y_, const __grid_cons
         ok = __all_sync(0xffffffffu, got);
         if (!ok) break;
         tc_fence_after();
-        const int n0 = (er.nt_begin + t) * kExpTileN;
-        const uint32_t ys = y_stage(s);
-        if (warp_live) {
-          // phase 1: lane = row.  out = y0 + scale * acc, rounded once, written back in place
-#pragma unroll 1
-          for (int c = 0; c < kExpTileN / 32; ++c) {
+        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 2);
+        const int n0 = (er.nt_begin + t) * er.tile_n;
+        if (ti.gather) {
+          // gathered rows: few rows, so add and store straight from registers.  The
+          // accumulator is handed back as soon as it sits in registers.
+          const int nch = er.ncbt == 4 ? 2 : 1;          // 32-column chunks of this warp: j, j + 4
+          for (int u = 0; u < nch; ++u) {
+            const int c = j + 4 * u;
             uint32_t r[32];
-            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * kExpTileN + c * 32, r);
-            tmem_ld_wait();
-            const uint32_t rowaddr = ys + (c >> 1) * (kTileM * 128) + row * 128;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int ch = (c & 1) * 4 + j;
-              const uint32_t addr = rowaddr + ((ch ^ (row & 7)) << 4);
-              float f[8];
-              unpack8<T>(lds128(addr), f);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = fmaf(scale, __uint_as_float(r[j * 8 + e]), f[e]);
-              sts128(addr, pack8<T>(f));
+            const uint32_t yrow_s = y_stage(s) + (c >> 1) * (kGatherRows * 128) + trow * 128 + (c & 1) * 64;
+            if (warp_live) {
+              tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + c * 32, r);
+              tmem_ld_wait();
             }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(ab));
-        if (warp_live) {
-          // phase 2: 4 rows x 128 bytes per instruction, rows of this segment only
+            if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 4 + u);
+            if (u == nch - 1) {                          // accumulator now lives in registers
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(ab));
+              if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 6);
+            }
+            if (warp_live && trow < ti.rows) {
 #pragma unroll
-          for (int cb = 0; cb < 2; ++cb) {
-            const int col = n0 + cb * kBoxCols + (lane & 7) * 8;
+              for (int k = 0; k < 4; ++k) {
+                const int col = n0 + c * 32 + k * 8;
+                if (col < h_out) {
+                  float f[8];
+                  unpack8<T>(lds128(yrow_s + k * 16), f);
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
-              const int rr = q * 32 + p * 4 + (lane >> 3);
-              if (rr < ti.rows && col < h_out) {
-                const uint4 val = lds128(ys + cb * (kTileM * 128) + rr * 128 + (((lane & 7) ^ (rr & 7)) << 4));
-                stg128(y + (int64_t)(ti.row0 + rr) * h_out + col, val);
+                  for (int e = 0; e < 8; ++e) f[e] = fmaf(scale, __uint_as_float(r[k * 8 + e]), f[e]);
+                  stg128(yout + col, pack8<T>(f));
+                }
               }
             }
           }
+          if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 7);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty_bar(s));
+          if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 3);
+          continue;
         }
+        // this warp's 32 x 32 block: 64 bytes per row inside column block j >> 1
+        const uint32_t blk = y_stage(s) + (j >> 1) * (kTileM * 128);
+        const int ch0 = (j & 1) * 4;
+        if (warp_live) {
+          // phase 1: lane = row.  out = y0 + scale * acc, rounded once, written back in place
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + j * 32, r);
+          const uint32_t rowaddr = blk + row * 128;
+          tmem_ld_wait();
+          if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 4);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float f[8];
+            unpack8<T>(lds128(rowaddr + (((ch0 + c) ^ (row & 7)) << 4)), f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = fmaf(scale, __uint_as_float(r[c * 8 + e]), f[e]);
+            sts128(rowaddr + (((ch0 + c) ^ (row & 7)) << 4), pack8<T>(f));
+          }
+        }
+        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 5);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(ab));
+        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 6);
+        if (warp_live) {
+          // phase 2: 8 rows x 64 bytes per instruction, rows of this segment only
+          const int col = n0 + (j >> 1) * kBoxCols + (ch0 + (lane & 3)) * 8;
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const int rr = q * 32 + p * 8 + (lane >> 2);
+            if (rr < ti.rows && col < h_out) {
+              const uint4 val = lds128(blk + rr * 128 + (((ch0 + (lane & 3)) ^ (rr & 7)) << 4));
+              stg128(y + (int64_t)tile_row(src, ti, rr) * h_out + col, val);
+            }
+          }
+        }
+        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 7);
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(s));
+        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 3);
       }
       ++li;
     }
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kExpMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
   if (threadIdx.x == 0 && abort_s) g_status = 1;
 }
@@ -598,6 +775,16 @@ int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int6
   return r == CUDA_SUCCESS ? VLR_OK : VLR_ERR_DRIVER;
 }
 
+int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, int64_t w_rows,
+                 int64_t cols, int dtype) {
+  int rc;
+  for (int i = 0; i < 3; ++i)
+    if ((rc = make_map_2d(&set->act[i], act, dtype, act_rows, cols, 32 << i)) != VLR_OK) return rc;
+  for (int i = 0; i < 4; ++i)
+    if ((rc = make_map_2d(&set->w[i], w, dtype, w_rows, cols, 16 << i)) != VLR_OK) return rc;
+  return VLR_OK;
+}
+
 // Split the output columns of a tile over several work items when there are too
 // few tiles to give every SM a few items.
 static int expand_splits(int64_t tiles, int h_out) {
@@ -607,6 +794,9 @@ static int expand_splits(int64_t tiles, int h_out) {
   if (want > ntiles) want = ntiles;
   return (int)want;
 }
+
+static long long* g_trace_ptr = nullptr;
+static int64_t g_trace_cap = 0;
 
 template <typename T>
 static int launch_atmm(void* y, const void* x, const void* w, const void* scales, TileSource src,
@@ -627,28 +817,24 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
   if (max_tiles <= 0 || n_problems <= 0) return VLR_OK;
   // In step mode (src.plan set) the tensor maps come from the plan in device
   // memory, h_in / h_out are maxima over its problems and only size the grid.
-  CUtensorMap map_act, map_w;
-  memset(&map_act, 0, sizeof(map_act));
-  memset(&map_w, 0, sizeof(map_w));
+  MapSet maps;
+  memset(&maps, 0, sizeof(maps));
+  src.trace = g_trace_ptr;
+  src.trace_cap = g_trace_cap;
   const bool step = src.plan != nullptr;
   int rc;
   if (h_in >= h_out) {
-    if (!step) {
-      if ((rc = make_map_2d(&map_act, x, dtype, T_rows, h_in, kBoxRowsAct)) != VLR_OK) return rc;
-      if ((rc = make_map_2d(&map_w, w, dtype, w_cells, h_in, kBoxRowsW)) != VLR_OK) return rc;
-    }
+    if (!step && (rc = make_map_set(&maps, x, T_rows, w, w_cells, h_in, dtype)) != VLR_OK) return rc;
     src.max_tiles = max_tiles;
     src.n_problems = n_problems;
     src.nsplit = 1;
     const int64_t items = max_tiles * n_problems;
     const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
     atmm_shrink_kernel<T><<<grid, kThreads, kShrinkSmem, stream>>>(
-        map_act, map_w, (T*)y, src, h_in, h_out, (flags & VLR_ATMM_ACCUMULATE_SHRINK) ? 1 : 0);
+        maps, (T*)y, (const T*)x, src, h_in, h_out,
+        (flags & VLR_ATMM_ACCUMULATE_SHRINK) ? 1 : 0);
   } else {
-    if (!step) {
-      if ((rc = make_map_2d(&map_act, y, dtype, T_rows, h_out, kBoxRowsAct)) != VLR_OK) return rc;
-      if ((rc = make_map_2d(&map_w, w, dtype, w_cells, h_out, kBoxRowsW)) != VLR_OK) return rc;
-    }
+    if (!step && (rc = make_map_set(&maps, y, T_rows, w, w_cells, h_out, dtype)) != VLR_OK) return rc;
     src.max_tiles = max_tiles;
     src.n_problems = n_problems;
     // in step mode the tile count lives on the device; with many problems no split is needed
@@ -656,8 +842,8 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
                       : expand_splits(max_tiles, h_out);
     const int64_t items = max_tiles * n_problems * src.nsplit;
     const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
-    atmm_expand_kernel<T><<<grid, kThreads, kExpSmem, stream>>>(
-        map_act, map_w, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in,
+    atmm_expand_kernel<T><<<grid, kExpThreads, kExpSmem, stream>>>(
+        maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in,
         (flags & VLR_ATMM_APPLY_SCALE) ? 1 : 0);
   }
   return launch_status();
@@ -717,4 +903,13 @@ extern "C" int vlr_device_status(int reset) {
     cudaMemcpyToSymbol(vlr::g_status, &z, sizeof(int));
   }
   return v;
+}
+
+// Debug aid: while a device buffer is set, CTA 0 of the tensor-core kernels writes
+// clock64 stamps into it (8 int64 per pipeline stage: stage issued, operands seen
+// by the MMA thread, MMAs issued / epilogue started, stage released).
+extern "C" int vlr_debug_set_trace(void* dev_buffer, int64_t n_int64) {
+  vlr::g_trace_ptr = reinterpret_cast<long long*>(dev_buffer);
+  vlr::g_trace_cap = dev_buffer ? n_int64 : 0;
+  return VLR_OK;
 }

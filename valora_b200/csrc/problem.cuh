@@ -9,11 +9,18 @@
 
 namespace vlr {
 
+// Tensor maps of one (activation, weight) pair.  All boxes are 64 columns (128
+// bytes, the swizzle span) wide; several box heights exist so that a tile is
+// fetched with few, large copies: activations 32 / 64 / 128 rows, weights
+// 16 / 32 / 64 / 128 rows.
+struct alignas(128) MapSet {
+  CUtensorMap act[3];
+  CUtensorMap w[4];
+};
+
 struct alignas(128) StepProblem {
-  CUtensorMap map_x;    // [max_rows, h_in]   box 32 rows x 64 columns
-  CUtensorMap map_wa;   // [cells_a, h_in]    box 16 rows x 64 columns
-  CUtensorMap map_y;    // [max_rows, h_out]  box 32 rows x 64 columns
-  CUtensorMap map_wb;   // [cells_b, h_out]   box 16 rows x 64 columns
+  MapSet shrink;        // act = x [max_rows, h_in],  w = A-side pool [cells_a, h_in]
+  MapSet expand;        // act = y [max_rows, h_out], w = B-side pool [cells_b, h_out]
   const void* x;
   void* y;
   const void* wa;       // A-side pool: cell = one rank row of length h_in
@@ -62,6 +69,8 @@ struct TileSource {
   // mode 1: packed schedule (int32 tile records + device counts)
   const int32_t* tiles;
   const int32_t* counts;
+  const int32_t* gather_rows;
+  int gather_mma;                    // 1: gather tiles are work items of the tensor-core kernels too
   // adapter tables
   const int64_t* a_start;
   const int64_t* a_loc;
@@ -73,6 +82,9 @@ struct TileSource {
   const StepProblem* plan;
   void* vbuf;
   int64_t vstride;
+  // optional timing trace of CTA 0 (clock64 stamps, 4 per pipeline stage); null = off
+  long long* trace;
+  int64_t trace_cap;
   // work decomposition, filled by the launcher
   int64_t max_tiles;                 // mode 0: upper bound of the tile count
   int n_problems;
@@ -83,6 +95,8 @@ int sm_count();
 
 // launchers shared between the single-problem entry points and the step entry point
 int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int box_rows);
+int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, int64_t w_rows,
+                 int64_t cols, int dtype);
 int bgmv_gather_launch(void* y, const void* x, const void* w, const void* scales,
                        const BgmvGroups& groups, int64_t max_groups, int h_in, int h_out,
                        int layout, int dtype, cudaStream_t stream, int n_problems);

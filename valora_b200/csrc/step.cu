@@ -22,18 +22,17 @@ extern "C" int vlr_step_plan_build(const vlr_problem_t* problems, int n_problems
     const vlr_problem_t& p = problems[i];
     if (!p.x || !p.y || !p.wa || !p.wb || !p.a_start_a || !p.a_loc_a || !p.a_start_b || !p.a_loc_b)
       return VLR_ERR_NULL;
-    if (p.h_in <= 0 || p.h_out <= 0 || p.h_in >= 65536 || p.h_out >= 65536 || (p.h_in & 7) ||
-        (p.h_out & 7))
+    // 64-column (128-byte) granularity: gathered rows are fetched in 128-byte pieces
+    if (p.h_in <= 0 || p.h_out <= 0 || p.h_in >= 65536 || p.h_out >= 65536 || (p.h_in & 63) ||
+        (p.h_out & 63))
       return VLR_ERR_SHAPE;
     if (p.cells_a <= 0 || p.cells_b <= 0 || p.slot_a < 0 || p.slot_b < 0) return VLR_ERR_RANGE;
     if (!aligned16(p.x) || !aligned16(p.y) || !aligned16(p.wa) || !aligned16(p.wb)) return VLR_ERR_ALIGN;
     StepProblem sp;
     memset(&sp, 0, sizeof(sp));
     int rc;
-    if ((rc = make_map_2d(&sp.map_x, p.x, dtype, max_rows, p.h_in, 32)) != VLR_OK) return rc;
-    if ((rc = make_map_2d(&sp.map_wa, p.wa, dtype, p.cells_a, p.h_in, 16)) != VLR_OK) return rc;
-    if ((rc = make_map_2d(&sp.map_y, p.y, dtype, max_rows, p.h_out, 32)) != VLR_OK) return rc;
-    if ((rc = make_map_2d(&sp.map_wb, p.wb, dtype, p.cells_b, p.h_out, 16)) != VLR_OK) return rc;
+    if ((rc = make_map_set(&sp.shrink, p.x, max_rows, p.wa, p.cells_a, p.h_in, dtype)) != VLR_OK) return rc;
+    if ((rc = make_map_set(&sp.expand, p.y, max_rows, p.wb, p.cells_b, p.h_out, dtype)) != VLR_OK) return rc;
     sp.x = p.x; sp.y = p.y; sp.wa = p.wa; sp.wb = p.wb;
     sp.a_start_a = p.a_start_a; sp.a_loc_a = p.a_loc_a;
     sp.a_start_b = p.a_start_b; sp.a_loc_b = p.a_loc_b;
@@ -76,6 +75,13 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   src.plan = plan;
   src.vbuf = vb;
   src.vstride = T * kMaxRank;
+  src.gather_rows = gather_rows;
+  src.gather_mma = (phase_mask & VLR_STEP_GATHER_ON_TENSOR_CORES) ? 1 : 0;
+  if (src.gather_mma) {
+    // gather tiles are work items of the two tensor-core launches
+    max_mma_tiles = T;
+    phase_mask &= ~(VLR_PHASE_SHRINK_GATHER | VLR_PHASE_EXPAND_GATHER);
+  }
   BgmvGroups g{};
   g.tiles = tiles;
   g.gather_rows = gather_rows;

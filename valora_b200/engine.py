@@ -26,8 +26,21 @@ from .pool import AdapterPool
 class LoraStepEngine:
     def __init__(self, projections: Sequence[Tuple[str, int, int]], ranks: Sequence[int],
                  scalings: Sequence[float], dtype, device, layers: int, max_tokens: int,
-                 tile_m: int = 128, mma_min_rows: int = 16, gather_rows_per_tile: int = 8,
-                 alloc_activations: bool = True):
+                 tile_m: int = 128, mma_min_rows: int = 16, gather_rows_per_tile: Optional[int] = None,
+                 alloc_activations: bool = True, gather_path: str = "mma"):
+        """gather_path: "mma" sends rows that are not consecutive in the batch (decode
+        tokens) through the tensor-core kernels with gathered rows (up to 128 rows of
+        an adapter per tile); "simt" sends them through the gather mat-vec kernels
+        (8 rows per tile)."""
+        if gather_path not in ("mma", "simt"):
+            raise ValueError("gather_path must be 'mma' or 'simt'")
+        self.gather_path = gather_path
+        if gather_rows_per_tile is None:
+            gather_rows_per_tile = 16 if gather_path == "mma" else 8
+        if gather_path == "simt" and gather_rows_per_tile > 8:
+            raise ValueError("the SIMT gather kernels take at most 8 rows per tile")
+        if gather_path == "mma" and gather_rows_per_tile > 16:
+            raise ValueError("a gather tile on the tensor-core path holds at most 16 rows")
         self.projections = list(projections)
         self.ranks = [int(r) for r in ranks]
         self.dtype, self.device = dtype, torch.device(device)
@@ -113,18 +126,28 @@ class LoraStepEngine:
     # ---- one step, inputs resident in HBM
     def step(self, tok_adapter: torch.Tensor, max_mma_tiles: int = 0, max_gather_tiles: int = 0):
         packed = self.packer.pack(tok_adapter, self.a_len, sort=True)
-        self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles)
+        self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles,
+                      phase_mask=ops.PHASE_ALL | self._gather_flag())
         return packed
+
+    def _gather_flag(self) -> int:
+        return ops.STEP_GATHER_ON_TENSOR_CORES if self.gather_path == "mma" else 0
+
+    def phases(self):
+        """(name, phase bit) of the kernel launches of one step, in order."""
+        if self.gather_path == "mma":
+            return [("shrink", ops.PHASE_SHRINK_MMA), ("expand", ops.PHASE_EXPAND_MMA)]
+        return [("shrink_mma", ops.PHASE_SHRINK_MMA), ("shrink_gather", ops.PHASE_SHRINK_GATHER),
+                ("expand_mma", ops.PHASE_EXPAND_MMA), ("expand_gather", ops.PHASE_EXPAND_GATHER)]
 
     def step_timed(self, tok_adapter: torch.Tensor, events):
         """Same work as step(), with a CUDA event recorded on the current stream
-        before the packer and after each of the five stages (events: 6 entries)."""
+        before the packer and after each stage (events: 2 + len(self.phases()))."""
         events[0].record()
         packed = self.packer.pack(tok_adapter, self.a_len, sort=True)
         events[1].record()
-        for i, phase in enumerate((ops.PHASE_SHRINK_MMA, ops.PHASE_SHRINK_GATHER,
-                                   ops.PHASE_EXPAND_MMA, ops.PHASE_EXPAND_GATHER)):
-            self.plan.run(packed, self.scales, 0, 0, phase_mask=phase)
+        for i, (_, phase) in enumerate(self.phases()):
+            self.plan.run(packed, self.scales, 0, 0, phase_mask=phase | self._gather_flag())
             events[2 + i].record()
         return packed
 

@@ -18,6 +18,7 @@ ATMM_ACCUMULATE_SHRINK, ATMM_APPLY_SCALE = 1, 2
 TILE_INTS, COUNT_INTS = 8, 8
 MAX_RANK = 128
 PHASE_SHRINK_MMA, PHASE_SHRINK_GATHER, PHASE_EXPAND_MMA, PHASE_EXPAND_GATHER, PHASE_ALL = 1, 2, 4, 8, 15
+STEP_GATHER_ON_TENSOR_CORES = 16
 
 
 def _dtype_code(t: torch.Tensor) -> int:
