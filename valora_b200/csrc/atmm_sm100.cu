@@ -408,9 +408,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
 // then a 3-stage ring streams (B tile, Y tile) pairs, 128 output columns each.
 // ============================================================================
 constexpr int kExpStages = 3;
-constexpr int kExpEpiWarps = 16;                       // 4 per TMEM lane quarter, 32 columns each
-constexpr int kExpEpiWarp0 = 0;                        // epilogue = warps 0..15
-constexpr int kExpProducers = 2;                       // producers = warps 16..17
+constexpr int kExpEpiWarps = 8;                        // 2 per TMEM lane quarter, 64 columns each
+constexpr int kExpEpiWarp0 = 0;                        // epilogue = warps 0..7
+constexpr int kExpProducers = 2;                       // producers = warps 8..9
 constexpr int kExpProdWarp0 = kExpEpiWarps;
 constexpr int kExpMmaWarp = kExpProdWarp0 + kExpProducers;   // warp 18
 constexpr int kExpThreads = 32 * (kExpMmaWarp + 1);
@@ -595,12 +595,14 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     }
   } else if (warp < kExpEpiWarps) {
     // ------------------------------------------------------------ V staging + epilogue
-    // 16 warps: warp (q, j) owns TMEM lanes 32q..32q+31 (rows) and columns 32j..32j+31
-    // of every 128-column output tile.
+    // 8 warps: warp (q, j) owns TMEM lanes 32q..32q+31 (rows) and the 64-column block j
+    // (and j + 2 of a 256-column gather tile) of every output tile.  With few warps each
+    // has registers to spare: both 32-column accumulator chunks and the eight Y pieces
+    // of a block are fetched before the first result is needed.
     const int q = warp & 3;                            // the lane quarter a warp may read
-    const int j = (warp - kExpEpiWarp0) >> 2;                     // its 32-column slice
+    const int j = (warp - kExpEpiWarp0) >> 2;          // its 64-column block
     const int row = q * 32 + lane;
-    const int et = threadIdx.x - 32 * kExpEpiWarp0;    // 0..511
+    const int et = threadIdx.x - 32 * kExpEpiWarp0;    // 0..255
     uint32_t it = 0, li = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
@@ -629,7 +631,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         const int vr = et & 127;                       // row slot
         const int vt = ti.gather ? ((vr & 31) < 4 ? (vr & 31) * 4 + (vr >> 5) : kTileM) : vr;
         const T* vrow = v + (int64_t)(vt < ti.rows ? tile_row(src, ti, vt) : 0) * v_pitch;
-        for (int c8 = et >> 7; c8 < k_pad / 8; c8 += 4) {
+        for (int c8 = et >> 7; c8 < k_pad / 8; c8 += kExpEpiWarps / 4) {
           uint4 val = make_uint4(0, 0, 0, 0);
           if (vt < ti.rows && c8 * 8 < ti.rank) val = ldg128(vrow + c8 * 8);
           sts128(a_tile + (c8 >> 3) * (kTileM * 128) + vr * 128 + (((c8 & 7) ^ (vr & 7)) << 4), val);
@@ -647,82 +649,89 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         tc_fence_after();
         if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 2);
         const int n0 = (er.nt_begin + t) * er.tile_n;
+        const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256;
         if (ti.gather) {
-          // gathered rows: few rows, so add and store straight from registers.  The
-          // accumulator is handed back as soon as it sits in registers.
-          const int nch = er.ncbt == 4 ? 2 : 1;          // 32-column chunks of this warp: j, j + 4
-          for (int u = 0; u < nch; ++u) {
-            const int c = j + 4 * u;
-            uint32_t r[32];
-            const uint32_t yrow_s = y_stage(s) + (c >> 1) * (kGatherRows * 128) + trow * 128 + (c & 1) * 64;
+          // gathered rows: few rows per lane quarter, so add and store straight from
+          // registers; the accumulator is handed back as soon as it sits in registers
+          const int nblk = er.ncbt >> 1;                 // 64-column blocks of this warp: j, j + 2
+          for (int u = 0; u < nblk; ++u) {
+            const int cb = j + 2 * u;
+            uint32_t r0[32], r1[32];
+            const uint32_t yrow_s = y_stage(s) + cb * (kGatherRows * 128) + trow * 128;
             if (warp_live) {
-              tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + c * 32, r);
+              tmem_ld_32x32(tacc + cb * 64, r0);
+              tmem_ld_32x32(tacc + cb * 64 + 32, r1);
               tmem_ld_wait();
             }
-            if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 4 + u);
-            if (u == nch - 1) {                          // accumulator now lives in registers
+            if (u == nblk - 1) {
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive(tempty_bar(ab));
-              if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 6);
             }
             if (warp_live && trow < ti.rows) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const int col = n0 + c * 32 + k * 8;
+              for (int c = 0; c < 8; ++c) {
+                const int col = n0 + cb * 64 + c * 8;
                 if (col < h_out) {
                   float f[8];
-                  unpack8<T>(lds128(yrow_s + k * 16), f);
+                  unpack8<T>(lds128(yrow_s + c * 16), f);
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) f[e] = fmaf(scale, __uint_as_float(r[k * 8 + e]), f[e]);
+                  for (int e = 0; e < 8; ++e)
+                    f[e] = fmaf(scale, __uint_as_float(c < 4 ? r0[c * 8 + e] : r1[(c - 4) * 8 + e]), f[e]);
                   stg128(yout + col, pack8<T>(f));
                 }
               }
             }
           }
-          if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 7);
           __syncwarp();
           if (lane == 0) mbar_arrive(empty_bar(s));
           if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 3);
           continue;
         }
-        // this warp's 32 x 32 block: 64 bytes per row inside column block j >> 1
-        const uint32_t blk = y_stage(s) + (j >> 1) * (kTileM * 128);
-        const int ch0 = (j & 1) * 4;
+        // consecutive rows: this warp's 32 rows x 64 columns = block j of the staged Y tile
+        const uint32_t blk = y_stage(s) + j * (kTileM * 128);
         if (warp_live) {
           // phase 1: lane = row.  out = y0 + scale * acc, rounded once, written back in place
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + j * 32, r);
+          uint32_t r0[32], r1[32];
+          uint4 yv[8];
+          tmem_ld_32x32(tacc + j * 64, r0);
+          tmem_ld_32x32(tacc + j * 64 + 32, r1);
           const uint32_t rowaddr = blk + row * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) yv[c] = lds128(rowaddr + ((c ^ (row & 7)) << 4));
           tmem_ld_wait();
-          if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 4);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 8; ++c) {
             float f[8];
-            unpack8<T>(lds128(rowaddr + (((ch0 + c) ^ (row & 7)) << 4)), f);
+            unpack8<T>(yv[c], f);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = fmaf(scale, __uint_as_float(r[c * 8 + e]), f[e]);
-            sts128(rowaddr + (((ch0 + c) ^ (row & 7)) << 4), pack8<T>(f));
+            for (int e = 0; e < 8; ++e)
+              f[e] = fmaf(scale, __uint_as_float(c < 4 ? r0[c * 8 + e] : r1[(c - 4) * 8 + e]), f[e]);
+            sts128(rowaddr + ((c ^ (row & 7)) << 4), pack8<T>(f));
           }
         }
-        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 5);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(ab));
-        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 6);
         if (warp_live) {
-          // phase 2: 8 rows x 64 bytes per instruction, rows of this segment only
-          const int col = n0 + (j >> 1) * kBoxCols + (ch0 + (lane & 3)) * 8;
+          // phase 2: 4 rows x 128 bytes per instruction, rows of this segment only
+          const int ch = lane & 7;
+          const int col = n0 + j * kBoxCols + ch * 8;
 #pragma unroll
-          for (int p = 0; p < 4; ++p) {
-            const int rr = q * 32 + p * 8 + (lane >> 2);
-            if (rr < ti.rows && col < h_out) {
-              const uint4 val = lds128(blk + rr * 128 + (((ch0 + (lane & 3)) ^ (rr & 7)) << 4));
-              stg128(y + (int64_t)tile_row(src, ti, rr) * h_out + col, val);
+          for (int half = 0; half < 2; ++half) {
+            uint4 ov[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const int rr = q * 32 + (half * 4 + p) * 4 + (lane >> 3);
+              ov[p] = lds128(blk + rr * 128 + ((ch ^ (rr & 7)) << 4));
+            }
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const int rr = q * 32 + (half * 4 + p) * 4 + (lane >> 3);
+              if (rr < ti.rows && col < h_out) stg128(y + (int64_t)(ti.row0 + rr) * h_out + col, ov[p]);
             }
           }
         }
-        if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 7);
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(s));
         if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 3);
