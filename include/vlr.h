@@ -229,6 +229,9 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
  * host-side upper bounds used to size the grids (surplus CTAs exit at once);
  * pass <= 0 for the safe bounds derived from T.  scales: dtype[n_adapters].
  * max_h_in / max_h_out: the largest h_in / h_out over the plan's problems.
+ * max_rank: the largest adapter rank the batch can contain (<= 0 or > 128 means 128).
+ * A bound of 64 or less lets the kernels run deeper operand rings; tiles whose rank
+ * exceeds the bound are skipped.
  * phase_mask: which of the four launches to enqueue (VLR_PHASE_ALL for a step;
  * single phases let a harness time each kernel on its own).
  */
@@ -246,7 +249,8 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
                   const int32_t* counts, const void* scales, int max_h_in, int max_h_out,
-                  int dtype, int phase_mask, void* workspace, size_t workspace_bytes, void* stream);
+                  int max_rank, int dtype, int phase_mask, void* workspace, size_t workspace_bytes,
+                  void* stream);
 
 #ifdef __cplusplus
 }

@@ -35,7 +35,7 @@ _SIGS = {
     "vlr_step_plan_bytes": (c_sz, [c_int]),
     "vlr_step_plan_build": (c_int, [c_vp, c_int, c_i64, c_int, c_vp]),
     "vlr_lora_step": (c_int, [c_vp, c_int, c_i64, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp,
-                              c_int, c_int, c_int, c_int, c_vp, c_sz, c_vp]),
+                              c_int, c_int, c_int, c_int, c_int, c_vp, c_sz, c_vp]),
     "vlr_lora_step_workspace_bytes": (c_sz, [c_i64, c_int]),
 }
 

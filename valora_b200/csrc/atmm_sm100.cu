@@ -57,7 +57,10 @@ struct TileInfo {
                      //    shrink: slot (i%4)*32 + (i/4)*8 - the first row of a swizzle atom, where
                      //            the 128-byte swizzle is the identity, so a plain 128-byte bulk
                      //            copy of the activation row lands in the right layout;
-                     //    expand: slot (i%4)*32 + i/4 (the V operand is written by generic stores).
+                     //    expand: the product is formed transposed, D^T = B^T V^T: the 128 output
+                     //            columns of a block are the M side (tensor-memory lanes), the
+                     //            gathered rows, dense in slots 0..15, are N = 16.  Every lane of
+                     //            every epilogue warp then carries useful outputs.
   int64_t wrow0;     // first pool cell of the slot
 };
 
@@ -150,7 +153,7 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
     }
   }
   if (ti.valid) {
-    if (ti.rank <= 0 || ti.rank > kMaxRank || (ti.rank & 7) || ti.rows <= 0 ||
+    if (ti.rank <= 0 || ti.rank > src.max_rank || (ti.rank & 7) || ti.rows <= 0 ||
         ti.rows > (ti.gather ? kGatherRows : kTileM)) {
       ti.valid = 0;                  // host validated what it could; skip bad entries
     } else {
@@ -189,13 +192,16 @@ __device__ __forceinline__ void trace_stamp(const TileSource& src, uint32_t k, i
 // shrink: persistent CTAs, 6-stage TMA ring over K, two accumulators in tensor
 // memory so the epilogue of one tile overlaps the main loop of the next.
 // ============================================================================
-constexpr int kShrinkStages = 6;
+// The operand ring is 192 KB; a stage is the X tile (16 KB) plus the weight rows
+// of the largest rank the launch may meet, so smaller ranks buy more stages
+// (rank 64: 8 stages of 24 KB, rank 128: 6 of 32 KB).  What bounds these kernels
+// is bytes in flight per SM against a memory latency of roughly 2 us under load.
+constexpr int kRingBytes = 192 * 1024;
+constexpr int kShrinkMaxStages = 12;
 constexpr int kShrinkXBytes = kTileM * 128;            // 16 KB
-constexpr int kShrinkWBytes = kMaxRank * 128;          // 16 KB
-constexpr int kShrinkStageBytes = kShrinkXBytes + kShrinkWBytes;
-constexpr int kShrinkSmem = 1024 + kShrinkStages * kShrinkStageBytes + 256;
+constexpr int kShrinkSmem = 1024 + kRingBytes + 512;
 
-template <typename T>
+template <typename T, int NST>
 __global__ void __launch_bounds__(kThreads, 1)
 atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
                    T* __restrict__ v_, const T* __restrict__ x_, TileSource src, int h_in_,
@@ -209,17 +215,19 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
   if ((int64_t)blockIdx.x >= total) return;            // nothing for this CTA: no TMEM taken
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + kShrinkStages * kShrinkStageBytes;
+  constexpr int nst = NST;                             // 6 stages of 32 KB or 8 of 24 KB
+  constexpr uint32_t stage_bytes = kRingBytes / NST;
+  const uint32_t bars = base + kRingBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (kShrinkStages + s); };
-  auto tfull_bar = [&](int ab) { return bars + 8u * (2 * kShrinkStages + ab); };
-  auto tempty_bar = [&](int ab) { return bars + 8u * (2 * kShrinkStages + 2 + ab); };
-  auto x_stage = [&](int s) { return base + (uint32_t)s * kShrinkStageBytes; };
-  auto w_stage = [&](int s) { return base + (uint32_t)s * kShrinkStageBytes + kShrinkXBytes; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kShrinkMaxStages + s); };
+  auto tfull_bar = [&](int ab) { return bars + 8u * (2 * kShrinkMaxStages + ab); };
+  auto tempty_bar = [&](int ab) { return bars + 8u * (2 * kShrinkMaxStages + 2 + ab); };
+  auto x_stage = [&](int s) { return base + (uint32_t)s * stage_bytes; };
+  auto w_stage = [&](int s) { return base + (uint32_t)s * stage_bytes + kShrinkXBytes; };
 
   if (threadIdx.x == 0) {
     abort_s = 0;
-    for (int s = 0; s < kShrinkStages; ++s) {
+    for (int s = 0; s < nst; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -267,9 +275,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
           (uint32_t)((ti.gather ? ti.rows : act_rows_loaded(ti.rows)) + n_pad) * 128u;
       for (int kb = 0; kb < kblocks; ++kb, ++kiter) {
         if ((int)(kiter % kShrinkProducers) != warp) continue;   // another producer's stage
-        const int s = kiter % kShrinkStages;
+        const int s = kiter % nst;
         if (lane == 0) {
-          ok = mbar_wait(empty_bar(s), ((kiter / kShrinkStages) & 1) ^ 1, &abort_s);
+          ok = mbar_wait(empty_bar(s), ((kiter / nst) & 1) ^ 1, &abort_s);
           if (ok) {
             trace_stamp(src, kiter, 0);
             mbar_expect_tx(full_bar(s), bytes);
@@ -293,9 +301,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     if (warp == 0 && lane == 0 && abort_s) {
       // drain: let every copy that was issued land before the CTA retires
       volatile int none = 0;
-      const uint32_t first = kiter > (uint32_t)kShrinkStages ? kiter - kShrinkStages : 0;
+      const uint32_t first = kiter > (uint32_t)nst ? kiter - nst : 0;
       for (uint32_t k = first; k < kiter; ++k)
-        mbar_wait(full_bar(k % kShrinkStages), (k / kShrinkStages) & 1, &none);
+        mbar_wait(full_bar(k % nst), (k / nst) & 1, &none);
     }
   } else if (warp == kShrinkMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
@@ -314,8 +322,8 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         ok = mbar_wait(tempty_bar(ab), ((li >> 1) & 1) ^ 1, &abort_s);
         if (ok) tc_fence_after();
         for (int kb = 0; kb < kblocks && ok; ++kb, ++kiter) {
-          const int s = kiter % kShrinkStages;
-          ok = mbar_wait(full_bar(s), (kiter / kShrinkStages) & 1, &abort_s);
+          const int s = kiter % nst;
+          ok = mbar_wait(full_bar(s), (kiter / nst) & 1, &abort_s);
           if (!ok) break;
           trace_stamp(src, kiter, 1);
           tc_fence_after();
@@ -407,7 +415,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
 // expand: persistent CTAs; per tile the V rows are staged once as the A operand,
 // then a 3-stage ring streams (B tile, Y tile) pairs, 128 output columns each.
 // ============================================================================
-constexpr int kExpStages = 3;
+constexpr int kExpMaxStages = 4;
 constexpr int kExpEpiWarps = 8;                        // 2 per TMEM lane quarter, 64 columns each
 constexpr int kExpEpiWarp0 = 0;                        // epilogue = warps 0..7
 constexpr int kExpProducers = 2;                       // producers = warps 8..9
@@ -416,23 +424,26 @@ constexpr int kExpMmaWarp = kExpProdWarp0 + kExpProducers;   // warp 18
 constexpr int kExpThreads = 32 * (kExpMmaWarp + 1);
 constexpr int kExpTileN = 128;
 constexpr int kExpABytes = 2 * kTileM * 128;           // V tile, two 64-column K blocks: 32 KB
-constexpr int kExpBBytes = 2 * kMaxRank * 128;         // two 64-column N blocks x 128 rows: 32 KB
-constexpr int kExpYBytes = 2 * kTileM * 128;           // two 64-column blocks x 128 rows: 32 KB
-constexpr int kExpStageBytes = kExpBBytes + kExpYBytes;
-constexpr int kExpSmem = 1024 + kExpABytes + kExpStages * kExpStageBytes + 256;
+// A stage holds the B rows of its columns (64-column blocks k_pad * 128 bytes apart)
+// followed by the Y rows: 16 + 32 KB for a 128-row tile of rank <= 64, 32 + 32 KB at
+// rank 128, 32 + 8 KB for a 256-column gather tile.  Launches that cannot meet a rank
+// above 64 run four 48 KB stages, the others three 64 KB stages.
+constexpr int kExpAccBufs = 4;                         // accumulators of 128 TMEM columns
+constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512;
 
 // A work item's output tiles.  Consecutive-row tiles use 128 columns per stage
 // (B 64-column blocks 16 KB apart).  Gather tiles stream almost only weights, so
 // with rank <= 64 they take 256 columns per stage (blocks 8 KB apart): twice the
 // bytes in flight per stage.
-struct ExpRange { int nt_begin, nt_count, h_out, ncbt, tile_n; uint32_t bstride; };
+struct ExpRange { int nt_begin, nt_count, h_out, ncbt, tile_n; uint32_t bstride, yoff; };
 
 __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileInfo& ti, int h_out_) {
   ExpRange r;
   r.h_out = src.plan ? src.plan[ti.problem].h_out : h_out_;
   r.ncbt = (ti.gather && ti.rank <= 64) ? 4 : 2;
   r.tile_n = r.ncbt * kBoxCols;
-  r.bstride = (uint32_t)(kExpBBytes / r.ncbt);
+  r.bstride = (uint32_t)(((ti.rank + 15) & ~15) * 128);
+  r.yoff = (uint32_t)r.ncbt * r.bstride;
   const int ntiles = (r.h_out + r.tile_n - 1) / r.tile_n;
   const int per = (ntiles + src.nsplit - 1) / src.nsplit;
   r.nt_begin = ti.split * per;
@@ -440,7 +451,7 @@ __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileI
   return r;
 }
 
-template <typename T>
+template <typename T, int NST>
 __global__ void __launch_bounds__(kExpThreads, 1)
 atmm_expand_kernel(const __grid_constant__ MapSet maps_,
                    T* __restrict__ y_, const T* __restrict__ v_, const T* __restrict__ scales,
@@ -455,23 +466,24 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t a_tile = base;
-  auto b_stage = [&](int s) { return base + kExpABytes + (uint32_t)s * kExpStageBytes; };
-  auto y_stage = [&](int s) { return base + kExpABytes + (uint32_t)s * kExpStageBytes + kExpBBytes; };
-  const uint32_t bars = base + kExpABytes + kExpStages * kExpStageBytes;
+  constexpr int nst = NST;                             // 3 stages of 64 KB or 4 of 48 KB
+  constexpr uint32_t stage_bytes = kRingBytes / NST;
+  auto b_stage = [&](int s) { return base + kExpABytes + (uint32_t)s * stage_bytes; };
+  const uint32_t bars = base + kExpABytes + kRingBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (kExpStages + s); };
-  auto tfull_bar = [&](int ab) { return bars + 8u * (2 * kExpStages + ab); };
-  auto tempty_bar = [&](int ab) { return bars + 8u * (2 * kExpStages + 2 + ab); };
-  const uint32_t a_ready_bar = bars + 8u * (2 * kExpStages + 4);
-  const uint32_t a_free_bar = bars + 8u * (2 * kExpStages + 5);
+  auto empty_bar = [&](int s) { return bars + 8u * (kExpMaxStages + s); };
+  auto tfull_bar = [&](int ab) { return bars + 8u * (2 * kExpMaxStages + ab); };
+  auto tempty_bar = [&](int ab) { return bars + 8u * (2 * kExpMaxStages + kExpAccBufs + ab); };
+  const uint32_t a_ready_bar = bars + 8u * (2 * kExpMaxStages + 2 * kExpAccBufs);
+  const uint32_t a_free_bar = bars + 8u * (2 * kExpMaxStages + 2 * kExpAccBufs + 1);
 
   if (threadIdx.x == 0) {
     abort_s = 0;
-    for (int s = 0; s < kExpStages; ++s) {
+    for (int s = 0; s < nst; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), kExpEpiWarps);
     }
-    for (int ab = 0; ab < 2; ++ab) {
+    for (int ab = 0; ab < kExpAccBufs; ++ab) {
       mbar_init(tfull_bar(ab), 1);
       mbar_init(tempty_bar(ab), kExpEpiWarps);
     }
@@ -509,11 +521,11 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       if (lane < 7) prefetch_tensormap(lane < 3 ? &ms->act[lane] : &ms->w[lane - 3]);
       for (int t = 0; t < er.nt_count; ++t, ++it) {
         if ((int)(it % kExpProducers) != pw) continue;            // the other producer's stage
-        const int s = it % kExpStages;
+        const int s = it % nst;
         const int n0 = (er.nt_begin + t) * er.tile_n;
         const int ncb = min(er.ncbt, (er.h_out - n0 + kBoxCols - 1) / kBoxCols);
         if (lane == 0) {
-          ok = mbar_wait(empty_bar(s), ((it / kExpStages) & 1) ^ 1, &abort_s);
+          ok = mbar_wait(empty_bar(s), ((it / nst) & 1) ^ 1, &abort_s);
           if (ok) {
             trace_stamp(src, it, 0);
             const uint32_t bytes = (uint32_t)ncb * (uint32_t)(k_pad + y_rows) * 128u;
@@ -523,7 +535,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
                           k_pad, full_bar(s));
             if (!ti.gather)
               for (int cb = 0; cb < ncb; ++cb)
-                load_act_rows(y_stage(s) + cb * (kTileM * 128), ms, n0 + cb * kBoxCols, ti.row0,
+                load_act_rows((b_stage(s) + er.yoff) + cb * (kTileM * 128), ms, n0 + cb * kBoxCols, ti.row0,
                               ti.rows, full_bar(s));
           }
         }
@@ -533,7 +545,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
           if (!ok) break;
           if (mine)
             for (int cb = 0; cb < ncb; ++cb)
-              bulk_load_1d(y_stage(s) + cb * (kGatherRows * 128) + lane * 128,
+              bulk_load_1d((b_stage(s) + er.yoff) + cb * (kGatherRows * 128) + lane * 128,
                            yrow + n0 + cb * kBoxCols, 128, full_bar(s));
         }
       }
@@ -542,9 +554,9 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     __syncwarp();
     if (pw == 0 && lane == 0 && abort_s) {
       volatile int none = 0;
-      const uint32_t first = it > (uint32_t)kExpStages ? it - kExpStages : 0;
+      const uint32_t first = it > (uint32_t)nst ? it - nst : 0;
       for (uint32_t k = first; k < it; ++k)
-        mbar_wait(full_bar(k % kExpStages), (k / kExpStages) & 1, &none);
+        mbar_wait(full_bar(k % nst), (k / nst) & 1, &none);
     }
   } else if (warp == kExpMmaWarp) {
     // ------------------------------------------------------------ MMA issuer
@@ -558,11 +570,12 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       const int k_pad = (ti.rank + 15) & ~15;
       const int ksteps = k_pad / 16;
       const uint32_t idesc = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, er.tile_n, 1);
+      const uint32_t idesc_g = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, kGatherRows, 0, 1);
       ok = __all_sync(0xffffffffu, mbar_wait(a_ready_bar, li & 1, &abort_s));
       for (int t = 0; t < er.nt_count && ok; ++t, ++it) {
-        const int s = it % kExpStages, ab = it & 1;
-        bool got = mbar_wait(full_bar(s), (it / kExpStages) & 1, &abort_s);
-        if (got) got = mbar_wait(tempty_bar(ab), ((it >> 1) & 1) ^ 1, &abort_s);
+        const int s = it % nst, ab = it & (kExpAccBufs - 1);
+        bool got = mbar_wait(full_bar(s), (it / nst) & 1, &abort_s);
+        if (got) got = mbar_wait(tempty_bar(ab), ((it >> 2) & 1) ^ 1, &abort_s);
         ok = __all_sync(0xffffffffu, got);             // the whole warp goes on or gives up
         if (!ok) break;
         if (k_pad != ti.rank) {
@@ -580,10 +593,23 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         tc_fence_after();
         if (lane == 0) {
           trace_stamp(src, it, 1);
-          for (int j = 0; j < ksteps; ++j) {
-            const uint64_t ad = smem_desc_sw128(a_tile + (j >> 2) * (kTileM * 128) + (j & 3) * 32, 16, 1024);
-            const uint64_t bd = smem_desc_sw128(b_stage(s) + j * (kBoxRowsW * 128), er.bstride, 1024);
-            umma_f16(tmem_base + ab * 256, ad, bd, idesc, j != 0);
+          if (ti.gather) {
+            // D^T[128 cols x 16 rows] = B^T[128 x k] * V^T[k x 16], one chain per 128 columns:
+            // A operand = the staged B tile read MN-major (two 64-column blocks bstride
+            // apart), B operand = the V rows, K-major, N = 16.
+            for (int mt = 0; mt < (er.ncbt >> 1); ++mt)
+              for (int j = 0; j < ksteps; ++j) {
+                const uint64_t ad = smem_desc_sw128(b_stage(s) + mt * 2 * er.bstride + j * (kBoxRowsW * 128),
+                                                    er.bstride, 1024);
+                const uint64_t bd = smem_desc_sw128(a_tile + (j >> 2) * (kTileM * 128) + (j & 3) * 32, 16, 1024);
+                umma_f16(tmem_base + ab * 128 + mt * 32, ad, bd, idesc_g, j != 0);
+              }
+          } else {
+            for (int j = 0; j < ksteps; ++j) {
+              const uint64_t ad = smem_desc_sw128(a_tile + (j >> 2) * (kTileM * 128) + (j & 3) * 32, 16, 1024);
+              const uint64_t bd = smem_desc_sw128(b_stage(s) + j * (kBoxRowsW * 128), er.bstride, 1024);
+              umma_f16(tmem_base + ab * 128, ad, bd, idesc, j != 0);
+            }
           }
           umma_commit(tfull_bar(ab));
         }
@@ -620,16 +646,21 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       }
       const int h_out = er.h_out;
       const int k_pad = (ti.rank + 15) & ~15;
-      // tile row held by this lane (gathered row i sits in slot (i%4)*32 + i/4)
-      const int trow = ti.gather ? (lane < 4 ? lane * 4 + q : kTileM) : row;
-      const bool warp_live = ti.gather ? q < ti.rows : q * 32 < ti.rows;
-      T* yout = y + (int64_t)(trow < ti.rows ? tile_row(src, ti, trow) : 0) * h_out;
+      // consecutive rows: lane = row.  Gather tiles: lane = output column (see the
+      // epilogue), warp j takes the j-th 128-column half of a stage.
+      const bool warp_live = ti.gather ? j < (er.ncbt >> 1) : q * 32 < ti.rows;
+      int grow[kGatherRows];
+      if (ti.gather) {
+#pragma unroll
+        for (int i = 0; i < kGatherRows; ++i)
+          grow[i] = i < ti.rows ? src.gather_rows[ti.row0 + i] : 0;
+      }
       // ---- stage V as the K-major, 128-byte-swizzled A operand (zeros beyond rank / rows)
       ok = __all_sync(0xffffffffu, mbar_wait(a_free_bar, (li & 1) ^ 1, &abort_s));
       if (!ok) break;
       {
         const int vr = et & 127;                       // row slot
-        const int vt = ti.gather ? ((vr & 31) < 4 ? (vr & 31) * 4 + (vr >> 5) : kTileM) : vr;
+        const int vt = vr;                             // gathered rows sit densely in slots 0..15
         const T* vrow = v + (int64_t)(vt < ti.rows ? tile_row(src, ti, vt) : 0) * v_pitch;
         for (int c8 = et >> 7; c8 < k_pad / 8; c8 += kExpEpiWarps / 4) {
           uint4 val = make_uint4(0, 0, 0, 0);
@@ -641,45 +672,39 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       }
       const float scale = apply_scale ? Elem<T>::to_float(scales[ti.adapter]) : 1.f;
       for (int t = 0; t < er.nt_count; ++t, ++it) {
-        const int s = it % kExpStages, ab = it & 1;
-        bool got = mbar_wait(full_bar(s), (it / kExpStages) & 1, &abort_s);
-        if (got) got = mbar_wait(tfull_bar(ab), (it >> 1) & 1, &abort_s);
+        const int s = it % nst, ab = it & (kExpAccBufs - 1);
+        bool got = mbar_wait(full_bar(s), (it / nst) & 1, &abort_s);
+        if (got) got = mbar_wait(tfull_bar(ab), (it >> 2) & 1, &abort_s);
         ok = __all_sync(0xffffffffu, got);
         if (!ok) break;
         tc_fence_after();
         if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 2);
         const int n0 = (er.nt_begin + t) * er.tile_n;
-        const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256;
+        const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * 128;
         if (ti.gather) {
-          // gathered rows: few rows per lane quarter, so add and store straight from
-          // registers; the accumulator is handed back as soon as it sits in registers
-          const int nblk = er.ncbt >> 1;                 // 64-column blocks of this warp: j, j + 2
-          for (int u = 0; u < nblk; ++u) {
-            const int cb = j + 2 * u;
-            uint32_t r0[32], r1[32];
-            const uint32_t yrow_s = y_stage(s) + cb * (kGatherRows * 128) + trow * 128;
-            if (warp_live) {
-              tmem_ld_32x32(tacc + cb * 64, r0);
-              tmem_ld_32x32(tacc + cb * 64 + 32, r1);
-              tmem_ld_wait();
-            }
-            if (u == nblk - 1) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(tempty_bar(ab));
-            }
-            if (warp_live && trow < ti.rows) {
+          // gathered rows, transposed product: this lane owns output column colt of the
+          // stage's tile and gets the 16 row values of that column from tensor memory
+          const int colt = j * 128 + q * 32 + lane;
+          const int col = n0 + colt;
+          uint32_t r[kGatherRows];
+          uint32_t yv[kGatherRows];
+          if (warp_live) {
+            tmem_ld_32x16(tacc + j * 32, r);
+            const uint32_t yaddr = (b_stage(s) + er.yoff) + (colt >> 6) * (kGatherRows * 128) + (colt & 63) * 2;
 #pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                const int col = n0 + cb * 64 + c * 8;
-                if (col < h_out) {
-                  float f[8];
-                  unpack8<T>(lds128(yrow_s + c * 16), f);
+            for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(yaddr + i * 128);
+            tmem_ld_wait();
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(ab));
+          if (warp_live && col < h_out) {
 #pragma unroll
-                  for (int e = 0; e < 8; ++e)
-                    f[e] = fmaf(scale, __uint_as_float(c < 4 ? r0[c * 8 + e] : r1[(c - 4) * 8 + e]), f[e]);
-                  stg128(yout + col, pack8<T>(f));
-                }
+            for (int i = 0; i < kGatherRows; ++i) {
+              if (i < ti.rows) {
+                const uint16_t y16 = (uint16_t)yv[i];
+                const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
+                y[(int64_t)grow[i] * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
               }
             }
           }
@@ -689,7 +714,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
           continue;
         }
         // consecutive rows: this warp's 32 rows x 64 columns = block j of the staged Y tile
-        const uint32_t blk = y_stage(s) + j * (kTileM * 128);
+        const uint32_t blk = (b_stage(s) + er.yoff) + j * (kTileM * 128);
         if (warp_live) {
           // phase 1: lane = row.  out = y0 + scale * acc, rounded once, written back in place
           uint32_t r0[32], r1[32];
@@ -807,19 +832,38 @@ static int expand_splits(int64_t tiles, int h_out) {
 static long long* g_trace_ptr = nullptr;
 static int64_t g_trace_cap = 0;
 
+static void size_rings(TileSource& src, int max_rank) {
+  if (max_rank <= 0 || max_rank > kMaxRank) max_rank = kMaxRank;
+  const int pad = (max_rank + 15) & ~15;
+  src.max_rank = max_rank;
+  src.shrink_stages = pad <= 64 ? 8 : 6;               // 24 KB or 32 KB per stage
+  src.shrink_stage_bytes = kRingBytes / src.shrink_stages;
+  src.exp_stages = pad <= 64 ? 4 : 3;                  // 48 KB or 64 KB per stage
+  src.exp_stage_bytes = kRingBytes / src.exp_stages;
+}
+
 template <typename T>
 static int launch_atmm(void* y, const void* x, const void* w, const void* scales, TileSource src,
                        int64_t max_tiles, int64_t T_rows, int h_in, int h_out, int64_t w_cells,
                        int dtype, int flags, cudaStream_t stream, int n_problems) {
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e1 = cudaFuncSetAttribute(atmm_shrink_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kShrinkSmem);
-    cudaError_t e2 = cudaFuncSetAttribute(atmm_shrink_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kShrinkSmem);
-    cudaError_t e3 = cudaFuncSetAttribute(atmm_expand_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kExpSmem);
-    cudaError_t e4 = cudaFuncSetAttribute(atmm_expand_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kExpSmem);
-    if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess || e4 != cudaSuccess) {
+    cudaError_t e = cudaSuccess;
+    auto set = [&](const void* f, int bytes) {
+      cudaError_t r = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      if (e == cudaSuccess) e = r;
+    };
+    set((const void*)atmm_shrink_kernel<__half, 6>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__half, 8>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__nv_bfloat16, 6>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__nv_bfloat16, 8>, kShrinkSmem);
+    set((const void*)atmm_expand_kernel<__half, 3>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__half, 4>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 3>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 4>, kExpSmem);
+    if (e != cudaSuccess) {
       cudaGetLastError();
-      return (int)(e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : e3 != cudaSuccess ? e3 : e4);
+      return (int)e;
     }
     attr_done = true;
   }
@@ -831,6 +875,8 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
   src.trace = g_trace_ptr;
   src.trace_cap = g_trace_cap;
   const bool step = src.plan != nullptr;
+  // rank bound: the caller's hint in a step, the width of the rank-side buffer otherwise
+  size_rings(src, step ? src.max_rank : (h_in >= h_out ? h_out : h_in));
   int rc;
   if (h_in >= h_out) {
     if (!step && (rc = make_map_set(&maps, x, T_rows, w, w_cells, h_in, dtype)) != VLR_OK) return rc;
@@ -839,9 +885,13 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
     src.nsplit = 1;
     const int64_t items = max_tiles * n_problems;
     const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
-    atmm_shrink_kernel<T><<<grid, kThreads, kShrinkSmem, stream>>>(
-        maps, (T*)y, (const T*)x, src, h_in, h_out,
-        (flags & VLR_ATMM_ACCUMULATE_SHRINK) ? 1 : 0);
+    const int acc = (flags & VLR_ATMM_ACCUMULATE_SHRINK) ? 1 : 0;
+    if (src.shrink_stages == 8)
+      atmm_shrink_kernel<T, 8><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
+                                                                        h_in, h_out, acc);
+    else
+      atmm_shrink_kernel<T, 6><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
+                                                                        h_in, h_out, acc);
   } else {
     if (!step && (rc = make_map_set(&maps, y, T_rows, w, w_cells, h_out, dtype)) != VLR_OK) return rc;
     src.max_tiles = max_tiles;
@@ -851,9 +901,13 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
                       : expand_splits(max_tiles, h_out);
     const int64_t items = max_tiles * n_problems * src.nsplit;
     const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
-    atmm_expand_kernel<T><<<grid, kExpThreads, kExpSmem, stream>>>(
-        maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in,
-        (flags & VLR_ATMM_APPLY_SCALE) ? 1 : 0);
+    const int sc = (flags & VLR_ATMM_APPLY_SCALE) ? 1 : 0;
+    if (src.exp_stages == 4)
+      atmm_expand_kernel<T, 4><<<grid, kExpThreads, kExpSmem, stream>>>(
+          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
+    else
+      atmm_expand_kernel<T, 3><<<grid, kExpThreads, kExpSmem, stream>>>(
+          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
   }
   return launch_status();
 }

@@ -89,6 +89,10 @@ struct TileSource {
   int64_t max_tiles;                 // mode 0: upper bound of the tile count
   int n_problems;
   int nsplit;                        // expand: work items per tile (column shares)
+  // operand rings, sized by the launcher from the largest rank the launch may meet
+  int max_rank;
+  int shrink_stages, shrink_stage_bytes;
+  int exp_stages, exp_stage_bytes;
 };
 
 int sm_count();

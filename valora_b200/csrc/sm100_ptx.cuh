@@ -202,17 +202,24 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
 // Bits: [4,6) D format (1 = f32), [7,10) A format, [10,13) B format (0 = f16,
 // 1 = bf16), 15 A major, 16 B major (0 = K-major, 1 = MN-major),
 // [17,23) N >> 3, [24,29) M >> 4.
-__device__ __forceinline__ uint32_t instr_desc_f16(int is_bf16, int n, int b_mn_major) {
+__device__ __forceinline__ uint32_t instr_desc_f16(int is_bf16, int n, int b_mn_major,
+                                                   int a_mn_major = 0) {
   uint32_t d = 0;
   d |= 1u << 4;
   d |= (is_bf16 ? 1u : 0u) << 7;
   d |= (is_bf16 ? 1u : 0u) << 10;
+  d |= (a_mn_major ? 1u : 0u) << 15;
   d |= (b_mn_major ? 1u : 0u) << 16;
   d |= (static_cast<uint32_t>(n) >> 3) << 17;
   d |= (128u >> 4) << 24;
   return d;
 }
 
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -51,7 +51,7 @@ extern "C" size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems) {
 extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                              const int32_t* gather_rows, int64_t max_mma_tiles,
                              int64_t max_gather_tiles, const int32_t* counts, const void* scales,
-                             int max_h_in, int max_h_out, int dtype, int phase_mask,
+                             int max_h_in, int max_h_out, int max_rank, int dtype, int phase_mask,
                              void* workspace, size_t workspace_bytes, void* stream) {
   if (T == 0 || n_problems == 0) return VLR_OK;
   if (!plan_dev || !tiles || !gather_rows || !counts || !scales || !workspace) return VLR_ERR_NULL;
@@ -76,6 +76,7 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   src.vbuf = vb;
   src.vstride = T * kMaxRank;
   src.gather_rows = gather_rows;
+  src.max_rank = (max_rank > 0 && max_rank <= kMaxRank) ? max_rank : kMaxRank;
   src.gather_mma = (phase_mask & VLR_STEP_GATHER_ON_TENSOR_CORES) ? 1 : 0;
   if (src.gather_mma) {
     // gather tiles are work items of the two tensor-core launches

@@ -127,7 +127,7 @@ class LoraStepEngine:
     def step(self, tok_adapter: torch.Tensor, max_mma_tiles: int = 0, max_gather_tiles: int = 0):
         packed = self.packer.pack(tok_adapter, self.a_len, sort=True)
         self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles,
-                      phase_mask=ops.PHASE_ALL | self._gather_flag())
+                      phase_mask=ops.PHASE_ALL | self._gather_flag(), max_rank=max(self.ranks))
         return packed
 
     def _gather_flag(self) -> int:
@@ -147,7 +147,8 @@ class LoraStepEngine:
         packed = self.packer.pack(tok_adapter, self.a_len, sort=True)
         events[1].record()
         for i, (_, phase) in enumerate(self.phases()):
-            self.plan.run(packed, self.scales, 0, 0, phase_mask=phase | self._gather_flag())
+            self.plan.run(packed, self.scales, 0, 0, phase_mask=phase | self._gather_flag(),
+                          max_rank=max(self.ranks))
             events[2 + i].record()
         return packed
 

@@ -319,7 +319,7 @@ class StepPlan:
         return self._ws
 
     def run(self, packed: Packed, scales: torch.Tensor, max_mma_tiles: int = 0,
-            max_gather_tiles: int = 0, phase_mask: int = PHASE_ALL):
+            max_gather_tiles: int = 0, phase_mask: int = PHASE_ALL, max_rank: int = 0):
         """Enqueue shrink + expand of every problem for the packed batch."""
         _check_input(scales, "scales")
         if scales.dtype != self.dtype:
@@ -330,7 +330,7 @@ class StepPlan:
         rc = self.lib.vlr_lora_step(_ptr(self.plan), self.n, packed.T, _ptr(packed.tiles),
                                     _ptr(packed.gather_rows), int(max_mma_tiles),
                                     int(max_gather_tiles), _ptr(packed.counts), _ptr(scales),
-                                    self.max_h_in, self.max_h_out,
+                                    self.max_h_in, self.max_h_out, int(max_rank),
                                     F16 if self.dtype == torch.float16 else BF16, int(phase_mask), _ptr(ws),
                                     ws.numel(), _stream(self.device))
         _lib.check(rc, "vlr_lora_step")
