@@ -30,7 +30,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-from valora_b200 import workloads  # noqa: E402
+from valora_b200 import shard, workloads  # noqa: E402
 
 METRIC = "lora_tokens_per_s"
 UNIT = "tokens/s"
@@ -280,14 +280,9 @@ def main():
     if ops.device_status() != 0:
         raise SystemExit("a bounded wait gave up inside a kernel during the timed region")
 
-    ms_per_step = total_ms / K
-    tokens = torch.tensor([float(T)], device=dev)
-    tmax = torch.tensor([ms_per_step], device=dev)
-    if dist is not None:
-        dist.all_reduce(tokens, op=dist.ReduceOp.SUM)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-    ms_per_step = float(tmax.item())
-    value = float(tokens.item()) / (ms_per_step * 1e-3)
+    # max over ranks of the device time, sum over ranks of the tokens served
+    ms_per_step, tokens = shard.reduce_timing(total_ms / K, float(T), device=dev)
+    value = tokens / (ms_per_step * 1e-3)
 
     # ---- end to end: pinned host buffers in, Y back out, every step
     e2e = None
@@ -308,12 +303,10 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         barrier()
-        ems = torch.tensor([e0.elapsed_time(e1) / args.e2e_steps], device=dev)
-        if dist is not None:
-            dist.all_reduce(ems, op=dist.ReduceOp.MAX)
-        e2e = {"value": float(tokens.item()) / (float(ems.item()) * 1e-3), "unit": UNIT,
+        ems, _ = shard.reduce_timing(e0.elapsed_time(e1) / args.e2e_steps, 0.0, device=dev)
+        e2e = {"value": tokens / (ems * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-               "ms_per_step": float(ems.item()),
+               "ms_per_step": ems,
                "note": "pinned host buffers of one layer are reused as the source and sink of every layer"}
 
     if rank != 0:
