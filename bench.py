@@ -289,17 +289,18 @@ def main():
     if args.e2e_steps > 0:
         xh = [torch.empty((T, hi), dtype=batch.dtype).pin_memory() for _, hi, _ in batch.projections]
         yh = [torch.empty((T, ho), dtype=batch.dtype).pin_memory() for _, _, ho in batch.projections]
+        oh = [torch.empty((T, ho), dtype=batch.dtype).pin_memory() for _, _, ho in batch.projections]
         for t in xh + yh:
             t.normal_()
         tok_h = torch.from_numpy(batch.tok_adapter.astype(np.int64)).pin_memory()
         tok_d = torch.empty(T, dtype=torch.int64, device=dev)
-        x_all, y_all = [xh] * args.layers, [yh] * args.layers
-        eng.step_host(tok_h, x_all, y_all, tok_d)
+        x_all, y_all, o_all = [xh] * args.layers, [yh] * args.layers, [oh] * args.layers
+        eng.step_host(tok_h, x_all, y_all, tok_d, y_out_host=o_all)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.e2e_steps):
-            h2d, d2h = eng.step_host(tok_h, x_all, y_all, tok_d)
+            h2d, d2h = eng.step_host(tok_h, x_all, y_all, tok_d, y_out_host=o_all)
         e1.record()
         torch.cuda.synchronize()
         barrier()
@@ -307,7 +308,8 @@ def main():
         e2e = {"value": tokens / (ems * 1e-3), "unit": UNIT,
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                "ms_per_step": ems,
-               "note": "pinned host buffers of one layer are reused as the source and sink of every layer"}
+               "note": "H2D, kernels and D2H pipelined by layer over three streams; one layer's pinned "
+                       "source buffers (read-only) and one layer's pinned sink buffers stand for all layers"}
 
     if rank != 0:
         if dist is not None:

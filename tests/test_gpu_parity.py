@@ -394,6 +394,42 @@ def test_step_all_gather_rows(ops, gather_path):
     _step_case(ops, workloads.config1(), [0], gather_path=gather_path)
 
 
+@pytest.mark.parametrize("overlap", [False, True])
+def test_step_from_host_buffers_matches_resident_step(ops, overlap):
+    """step_host (pinned host buffers in, Y out, optionally pipelined by layer over
+    three streams) gives bit for bit what step() gives on resident inputs, twice in
+    a row (the second call re-uses the device buffers the first one wrote)."""
+    from valora_b200.engine import LoraStepEngine
+    b = workloads.config0()
+    projs = [("q", 512, 512), ("up", 512, 1024)]
+    L = 3
+    eng = LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, L, b.T)
+    eng.randomize_weights(seed=5)
+    g = torch.Generator().manual_seed(9)
+    xh = [[torch.randn(b.T, hi, generator=g).to(b.dtype).pin_memory() for _, hi, _ in projs] for _ in range(L)]
+    yh = [[torch.randn(b.T, ho, generator=g).to(b.dtype).pin_memory() for _, _, ho in projs] for _ in range(L)]
+    out = [[torch.zeros(b.T, ho, dtype=b.dtype).pin_memory() for _, _, ho in projs] for _ in range(L)]
+    tok_h = torch.from_numpy(b.tok_adapter.astype(np.int64)).pin_memory()
+    tok_d = torch.empty(b.T, dtype=torch.int64, device=DEV)
+    # resident reference
+    for l in range(L):
+        for p in range(len(projs)):
+            eng.x[l][p].copy_(xh[l][p])
+            eng.y[l][p].copy_(yh[l][p])
+    eng.step(tok_h.to(DEV))
+    torch.cuda.synchronize()
+    want = [[eng.y[l][p].cpu() for p in range(len(projs))] for l in range(L)]
+    for _ in range(2):
+        h2d, d2h = eng.step_host(tok_h, xh, yh, tok_d, y_out_host=out, overlap=overlap)
+        torch.cuda.current_stream().synchronize()
+        assert ops.device_status() == 0
+        for l in range(L):
+            for p in range(len(projs)):
+                assert torch.equal(out[l][p], want[l][p]), (l, p)
+                out[l][p].zero_()
+    assert h2d == b.T * 8 + L * b.T * (512 + 512 + 512 + 1024) * 2 and d2h == L * b.T * (512 + 1024) * 2
+
+
 def test_step_gathered_rows_mixed_ranks(ops):
     """config 4 slice: 1024 adapters of ranks 16..128, mostly decode rows, many adapters
     with a handful of rows each - gathered tiles of every rank on the tensor cores"""

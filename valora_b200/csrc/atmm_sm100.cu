@@ -198,8 +198,24 @@ __device__ __forceinline__ void trace_stamp(const TileSource& src, uint32_t k, i
 // is bytes in flight per SM against a memory latency of roughly 2 us under load.
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kShrinkMaxStages = 12;
-constexpr int kShrinkXBytes = kTileM * 128;            // 16 KB
-constexpr int kShrinkSmem = 1024 + kRingBytes + 512;
+constexpr int kShrinkMaxSub = 4;                       // K blocks per stage, at most
+// The A operand of an MMA is a window of 128 rows (16 KB) from where a block's
+// activation rows start, whatever was loaded there: the window of the ring's last
+// block runs past the ring, so that much shared memory is allocated behind it.
+constexpr int kShrinkSmem = 1024 + kRingBytes + 512 + kTileM * 128;
+
+// A stage holds as many K blocks as fit: a block = the tile's activation rows
+// (2 KB for gathered rows, 4..16 KB for consecutive ones) then the adapter's rank
+// rows, both 64 columns wide.  Short tiles so keep as many bytes in flight as full ones.
+struct SubLayout { uint32_t xbytes, sub; int kbs; };
+__device__ __forceinline__ SubLayout sub_layout(const TileInfo& ti, int n_pad, uint32_t stage_bytes) {
+  SubLayout sl;
+  sl.xbytes = (uint32_t)(ti.gather ? kGatherRows : act_rows_loaded(ti.rows)) * 128u;
+  sl.sub = sl.xbytes + (uint32_t)n_pad * 128u;
+  const int k = (int)(stage_bytes / sl.sub);
+  sl.kbs = k < 1 ? 1 : (k > kShrinkMaxSub ? kShrinkMaxSub : k);
+  return sl;
+}
 
 template <typename T, int NST>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -223,7 +239,6 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
   auto tfull_bar = [&](int ab) { return bars + 8u * (2 * kShrinkMaxStages + ab); };
   auto tempty_bar = [&](int ab) { return bars + 8u * (2 * kShrinkMaxStages + 2 + ab); };
   auto x_stage = [&](int s) { return base + (uint32_t)s * stage_bytes; };
-  auto w_stage = [&](int s) { return base + (uint32_t)s * stage_bytes + kShrinkXBytes; };
 
   if (threadIdx.x == 0) {
     abort_s = 0;
@@ -257,7 +272,8 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
   if (warp < kShrinkProducers) {
     // ------------------------------------------------------------ producers (stage k -> warp k % 3)
     // lane 0: TMA boxes (weights; consecutive activation rows).  Gather tiles: lane i
-    // copies row i, 128 bytes per K block, with a 1-D bulk copy into row slot 8*i.
+    // fetches row i with a one-row box into row slot i; the copy engine applies the
+    // 128-byte swizzle from the address bits, so the slots form a dense tile.
     uint32_t kiter = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
@@ -268,21 +284,29 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       const int h_in = h_in_of(ti);
       const int n_pad = (ti.rank + 15) & ~15;
       const int kblocks = (h_in + kBoxCols - 1) / kBoxCols;
+      const SubLayout sl = sub_layout(ti, n_pad, stage_bytes);
+      const int nstages = (kblocks + sl.kbs - 1) / sl.kbs;
       const bool mine = ti.gather && lane < ti.rows;
-      const T* xrow = mine ? xg + (int64_t)src.gather_rows[ti.row0 + lane] * h_in : xg;
-      if (lane < 7) prefetch_tensormap(lane < 3 ? &ms->act[lane] : &ms->w[lane - 3]);
-      const uint32_t bytes =
+      const int grow = mine ? src.gather_rows[ti.row0 + lane] : 0;
+      if (lane < 8) prefetch_tensormap(lane < 3 ? &ms->act[lane] : lane < 7 ? &ms->w[lane - 3] : &ms->row);
+      const uint32_t blk_bytes =
           (uint32_t)((ti.gather ? ti.rows : act_rows_loaded(ti.rows)) + n_pad) * 128u;
-      for (int kb = 0; kb < kblocks; ++kb, ++kiter) {
+      for (int st = 0; st < nstages; ++st, ++kiter) {
         if ((int)(kiter % kShrinkProducers) != warp) continue;   // another producer's stage
         const int s = kiter % nst;
+        const int kb0 = st * sl.kbs;
+        const int nsub = min(sl.kbs, kblocks - kb0);
         if (lane == 0) {
           ok = mbar_wait(empty_bar(s), ((kiter / nst) & 1) ^ 1, &abort_s);
           if (ok) {
             trace_stamp(src, kiter, 0);
-            mbar_expect_tx(full_bar(s), bytes);
-            if (!ti.gather) load_act_rows(x_stage(s), ms, kb * kBoxCols, ti.row0, ti.rows, full_bar(s));
-            load_w_rows(w_stage(s), ms, kb * kBoxCols, (int)ti.wrow0, n_pad, full_bar(s));
+            mbar_expect_tx(full_bar(s), blk_bytes * nsub);
+            for (int j = 0; j < nsub; ++j) {
+              const uint32_t sb = x_stage(s) + j * sl.sub;
+              const int c0 = (kb0 + j) * kBoxCols;
+              if (!ti.gather) load_act_rows(sb, ms, c0, ti.row0, ti.rows, full_bar(s));
+              load_w_rows(sb + sl.xbytes, ms, c0, (int)ti.wrow0, n_pad, full_bar(s));
+            }
             trace_stamp(src, kiter, 3);
           }
         }
@@ -291,8 +315,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
           ok = __shfl_sync(0xffffffffu, ok, 0);        // also orders expect_tx before the copies
           if (!ok) break;
           if (mine)
-            bulk_load_1d(x_stage(s) + ((lane & 3) * 32 + (lane >> 2) * 8) * 128, xrow + kb * kBoxCols,
-                         128, full_bar(s));
+            for (int j = 0; j < nsub; ++j)
+              tma_load_2d(x_stage(s) + j * sl.sub + lane * 128, &ms->row, (kb0 + j) * kBoxCols, grow,
+                          full_bar(s));
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -321,17 +346,24 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         const int astr = acc_stride(n_pad), nacc = 256 / astr;
         ok = mbar_wait(tempty_bar(ab), ((li >> 1) & 1) ^ 1, &abort_s);
         if (ok) tc_fence_after();
-        for (int kb = 0; kb < kblocks && ok; ++kb, ++kiter) {
+        const SubLayout sl = sub_layout(ti, n_pad, stage_bytes);
+        const int nstages = (kblocks + sl.kbs - 1) / sl.kbs;
+        uint32_t ks = 0;                               // K slices of this tile issued so far
+        for (int st = 0; st < nstages && ok; ++st, ++kiter) {
           const int s = kiter % nst;
           ok = mbar_wait(full_bar(s), (kiter / nst) & 1, &abort_s);
           if (!ok) break;
           trace_stamp(src, kiter, 1);
           tc_fence_after();
+          const int nsub = min(sl.kbs, kblocks - st * sl.kbs);
+          for (int j = 0; j < nsub; ++j) {
+            const uint32_t sb = x_stage(s) + j * sl.sub;
 #pragma unroll
-          for (int k = 0; k < kBoxCols / 16; ++k) {
-            const uint64_t ad = smem_desc_sw128(x_stage(s) + k * 32, 16, 1024);
-            const uint64_t bd = smem_desc_sw128(w_stage(s) + k * 32, 16, 1024);
-            umma_f16(tacc + (k % nacc) * astr, ad, bd, idesc, (kb * (kBoxCols / 16) + k) >= nacc);
+            for (int k = 0; k < kBoxCols / 16; ++k, ++ks) {
+              const uint64_t ad = smem_desc_sw128(sb + k * 32, 16, 1024);
+              const uint64_t bd = smem_desc_sw128(sb + sl.xbytes + k * 32, 16, 1024);
+              umma_f16(tacc + (ks & (nacc - 1)) * astr, ad, bd, idesc, ks >= (uint32_t)nacc);
+            }
           }
           umma_commit(empty_bar(s));
           trace_stamp(src, kiter, 2);
@@ -359,9 +391,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         v_pitch = kMaxRank;
       }
       const int n_pad = (ti.rank + 15) & ~15;
-      // tile row held by this lane: slot = row for consecutive rows, slot 8*i for gathered row i
-      const int trow = ti.gather ? (((lane & 7) == 0 && lane < 32) ? (lane >> 3) * 4 + q : kTileM) : row;
-      const bool warp_live = ti.gather ? q < ti.rows : q * 32 < ti.rows;
+      // tile row held by this lane (gathered rows sit in slots 0..15: lane quarter 0)
+      const int trow = ti.gather ? (q == 0 && lane < kGatherRows ? lane : kTileM) : row;
+      const bool warp_live = ti.gather ? q == 0 : q * 32 < ti.rows;
       if (warp_live) {
         T* vrow = v + (int64_t)(trow < ti.rows ? tile_row(src, ti, trow) : 0) * v_pitch;
         const int astr = acc_stride(n_pad), nacc = 256 / astr;
@@ -816,7 +848,7 @@ int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, 
     if ((rc = make_map_2d(&set->act[i], act, dtype, act_rows, cols, 32 << i)) != VLR_OK) return rc;
   for (int i = 0; i < 4; ++i)
     if ((rc = make_map_2d(&set->w[i], w, dtype, w_rows, cols, 16 << i)) != VLR_OK) return rc;
-  return VLR_OK;
+  return make_map_2d(&set->row, act, dtype, act_rows, cols, 1);
 }
 
 // Split the output columns of a tile over several work items when there are too

@@ -1,7 +1,10 @@
 // Decode gather mat-vec (BGMV) for sm_100a: bandwidth-bound SIMT kernels.
 //
 // Two addressing modes share the kernels:
-//  * token mode  - group g is token g, adapter = indicies[g] (the drop-in call);
+//  * token mode  - the drop-in call: adapter = indicies[token].  The tokens of one
+//    adapter inside a window of 1024 tokens are served G at a time by the work
+//    item of the first of them (the other tokens' items return at once), so an
+//    adapter's rows cross L2 -> SM once per G tokens and not once per token;
 //  * gather mode - group g is a gather tile of the packed schedule: up to G rows
 //    of one adapter, listed in gather_rows, so the adapter's rows are fetched
 //    from HBM once per group instead of once per token.
@@ -97,6 +100,59 @@ __device__ __forceinline__ void resolve_item(const BgmvGroups& g, int64_t item, 
 }
 
 constexpr int kThreadsBgmv = 256;
+constexpr int kGroupWindow = 1024;                    // tokens searched for same-adapter peers
+
+// Block-wide form of resolve_item; every thread calls it and the result is in
+// *out after it returns.  Token mode with G > 1 groups tokens by adapter: the
+// block marks the tokens of its window that share the item token's adapter
+// (one ballot per 32 tokens), then thread 0 counts those before the token -
+// the token leads a group iff that count is a multiple of G - and lists the
+// group's rows, in batch order.  Items of tokens that lead no group get nrows 0.
+template <typename T, int G>
+__device__ __forceinline__ void resolve_block(const BgmvGroups& g, int64_t item, int64_t n_groups,
+                                              int n_slices, T* y, const T* x, const T* w, int h_in,
+                                              int h_out, bool expand, Item<T, G>* out,
+                                              uint32_t* mask_s) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (G == 1 || g.tiles != nullptr) {
+    if (tid == 0) resolve_item<T, G>(g, item, n_groups, n_slices, y, x, w, h_in, h_out, expand, out);
+    __syncthreads();
+    return;
+  }
+  const int64_t t = (item / n_slices) % n_groups;
+  const int64_t w0 = t - t % kGroupWindow;
+  const int wn = (int)min((int64_t)kGroupWindow, g.batch - w0);
+  const int64_t a = g.indicies[t];
+  for (int c0 = tid & ~31; c0 < kGroupWindow; c0 += kThreadsBgmv) {
+    const int u = c0 + lane;
+    const bool m = u < wn && g.indicies[w0 + u] == a;
+    const unsigned b = __ballot_sync(0xffffffffu, m);
+    if (lane == 0) mask_s[c0 >> 5] = b;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    resolve_item<T, G>(g, item, n_groups, n_slices, y, x, w, h_in, h_out, expand, out);
+    const int pos = (int)(t - w0);
+    int before = __popc(mask_s[pos >> 5] & ((1u << (pos & 31)) - 1u));
+    for (int i = 0; i < (pos >> 5); ++i) before += __popc(mask_s[i]);
+    int n = 0;
+    if (before % G == 0) {
+      int wd = pos >> 5;
+      uint32_t bits = mask_s[wd] & ~((1u << (pos & 31)) - 1u);
+      while (n < G) {
+        while (bits == 0 && ++wd < kGroupWindow / 32) bits = mask_s[wd];
+        if (bits == 0) break;
+        const int b = __ffs(bits) - 1;
+        bits &= bits - 1;
+        out->rows[n++] = (int)(w0 + wd * 32 + b);
+      }
+    }
+    for (int i = n; i < G; ++i) out->rows[i] = -1;
+    out->nrows = n;
+  }
+  __syncthreads();
+}
+
 constexpr int kWarpsBgmv = kThreadsBgmv / 32;
 constexpr int kShrinkKB = 2048;                       // activation elements staged per pass
 
@@ -108,6 +164,7 @@ bgmv_shrink_kernel(T* __restrict__ y_, const T* __restrict__ x_, const T* __rest
                    BgmvGroups groups, int h_in_, int y_pitch_, int n_slices, int n_problems) {
   __shared__ __align__(16) T xs[G][kShrinkKB];
   __shared__ Item<T, G> item_s;
+  __shared__ uint32_t mask_s[kGroupWindow / 32];
   constexpr int kSlice = kWarpsBgmv * R;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -116,8 +173,7 @@ bgmv_shrink_kernel(T* __restrict__ y_, const T* __restrict__ x_, const T* __rest
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
     __syncthreads();                                   // previous item done with item_s / xs
-    if (tid == 0) resolve_item<T, G>(groups, item, n_groups, n_slices, y_, x_, w_, h_in_, y_pitch_, false, &item_s);
-    __syncthreads();
+    resolve_block<T, G>(groups, item, n_groups, n_slices, y_, x_, w_, h_in_, y_pitch_, false, &item_s, mask_s);
     const int rank = item_s.rank, nrows = item_s.nrows;
     const int slice0 = item_s.slice * kSlice;
     if (nrows == 0 || slice0 >= rank) continue;
@@ -200,6 +256,7 @@ bgmv_expand_rows_kernel(T* __restrict__ y_, const T* __restrict__ v_, const T* _
   __shared__ float vs[G][kMaxRank];
   __shared__ int64_t rowoff[kMaxRank];
   __shared__ Item<T, G> item_s;
+  __shared__ uint32_t mask_s[kGroupWindow / 32];
 
   const int tid = threadIdx.x;
   const int64_t n_groups = n_groups_of(groups);
@@ -207,8 +264,7 @@ bgmv_expand_rows_kernel(T* __restrict__ y_, const T* __restrict__ v_, const T* _
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
     __syncthreads();
-    if (tid == 0) resolve_item<T, G>(groups, item, n_groups, n_slices, y_, v_, w_, v_pitch_, h_out_, true, &item_s);
-    __syncthreads();
+    resolve_block<T, G>(groups, item, n_groups, n_slices, y_, v_, w_, v_pitch_, h_out_, true, &item_s, mask_s);
     const int rank = item_s.rank, nrows = item_s.nrows;
     const int h_out = item_s.pv.h_out, v_pitch = item_s.pv.h_in;
     const int o = (item_s.slice * kThreadsBgmv + tid) * 8;
@@ -276,6 +332,7 @@ bgmv_expand_punica_kernel(T* __restrict__ y_, const T* __restrict__ v_, const T*
   __shared__ float vs[G][kMaxRank];
   __shared__ int64_t rowoff[kMaxRank];
   __shared__ Item<T, G> item_s;
+  __shared__ uint32_t mask_s[kGroupWindow / 32];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t n_groups = n_groups_of(groups);
@@ -283,8 +340,7 @@ bgmv_expand_punica_kernel(T* __restrict__ y_, const T* __restrict__ v_, const T*
 
   for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
     __syncthreads();
-    if (tid == 0) resolve_item<T, G>(groups, item, n_groups, n_slices, y_, v_, w_, v_pitch_, h_out_, true, &item_s);
-    __syncthreads();
+    resolve_block<T, G>(groups, item, n_groups, n_slices, y_, v_, w_, v_pitch_, h_out_, true, &item_s, mask_s);
     const int rank = item_s.rank, nrows = item_s.nrows;
     const int h_out = item_s.pv.h_out, v_pitch = item_s.pv.h_in;
     const int o_begin = item_s.slice * kPunicaCols;
@@ -421,10 +477,10 @@ extern "C" int vlr_bgmv(void* y, const void* x, const void* w, const int64_t* a_
   g.qkvo = qkvo;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == VLR_F16)
-    return launch_bgmv<__half, 1, 2>((__half*)y, (const __half*)x, (const __half*)w,
+    return launch_bgmv<__half, 8, 2>((__half*)y, (const __half*)x, (const __half*)w,
                                      (const __half*)lora_scales, g, batch, (int)h_in, (int)h_out,
                                      layout, s, 1);
-  return launch_bgmv<__nv_bfloat16, 1, 2>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,
+  return launch_bgmv<__nv_bfloat16, 8, 2>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,
                                           (const __nv_bfloat16*)w,
                                           (const __nv_bfloat16*)lora_scales, g, batch, (int)h_in,
                                           (int)h_out, layout, s, 1);

@@ -14,8 +14,9 @@ namespace vlr {
 // fetched with few, large copies: activations 32 / 64 / 128 rows, weights
 // 16 / 32 / 64 / 128 rows.
 struct alignas(128) MapSet {
-  CUtensorMap act[3];
-  CUtensorMap w[4];
+  CUtensorMap act[3];   // boxes of 32 / 64 / 128 activation rows x 64 columns
+  CUtensorMap w[4];     // boxes of 16 / 32 / 64 / 128 pool cells x 64 columns
+  CUtensorMap row;      // one activation row x 64 columns (gathered rows)
 };
 
 struct alignas(128) StepProblem {

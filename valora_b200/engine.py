@@ -71,6 +71,7 @@ class LoraStepEngine:
         self.x: List[List[torch.Tensor]] = []
         self.y: List[List[torch.Tensor]] = []
         self.plan: Optional[ops.StepPlan] = None
+        self._copy_in = self._copy_out = None
         if alloc_activations:
             for _ in range(self.layers):
                 self.x.append([torch.zeros((self.max_tokens, hi), dtype=dtype, device=self.device)
@@ -155,22 +156,59 @@ class LoraStepEngine:
     # ---- one step from host buffers (pinned): H2D, step, D2H
     def step_host(self, tok_adapter_host: torch.Tensor, x_host: Sequence[Sequence[torch.Tensor]],
                   y_host: Sequence[Sequence[torch.Tensor]], tok_dev: torch.Tensor,
-                  max_mma_tiles: int = 0, max_gather_tiles: int = 0):
-        """x_host[layer][p] / y_host[layer][p] are pinned host tensors of T rows;
-        y_host is read as Y0 and overwritten with Y.  Returns bytes copied
-        (h2d, d2h).  All copies and kernels are enqueued on the current stream."""
+                  max_mma_tiles: int = 0, max_gather_tiles: int = 0,
+                  y_out_host: Optional[Sequence[Sequence[torch.Tensor]]] = None, overlap: bool = True):
+        """x_host[layer][p] / y_host[layer][p] are pinned host tensors of T rows; Y0 is
+        read from y_host and Y is written to y_out_host (default: back into y_host).
+        Returns the bytes copied (h2d, d2h).
+
+        overlap=True pipelines by layer over three streams: a copy-in stream runs
+        ahead with the next layers' X and Y0, the current stream packs the batch once
+        and runs each layer's problems as soon as its inputs have landed, and a
+        copy-out stream drains finished layers - the PCIe link is busy in both
+        directions at once.  The current stream waits for the copy-out stream at the
+        end, so synchronising it covers the whole step.  overlap=False enqueues
+        everything on the current stream."""
         T = tok_adapter_host.numel()
+        y_out_host = y_host if y_out_host is None else y_out_host
+        n_proj = len(self.projections)
         h2d = d2h = 0
+        cur = torch.cuda.current_stream(self.device)
+        if overlap:
+            if self._copy_in is None:
+                self._copy_in = torch.cuda.Stream(self.device)
+                self._copy_out = torch.cuda.Stream(self.device)
+            s_in, s_out = self._copy_in, self._copy_out
+            s_in.wait_stream(cur)          # earlier work on the buffers (a previous step) is done
+            s_out.wait_stream(cur)
+        else:
+            s_in = s_out = cur
         tok_dev[:T].copy_(tok_adapter_host, non_blocking=True)
         h2d += T * 8
+        packed = self.packer.pack(tok_dev[:T], self.a_len, sort=True)
+        flags = ops.PHASE_ALL | self._gather_flag()
         for layer in range(self.layers):
-            for p in range(len(self.projections)):
-                self.x[layer][p][:T].copy_(x_host[layer][p][:T], non_blocking=True)
-                self.y[layer][p][:T].copy_(y_host[layer][p][:T], non_blocking=True)
-                h2d += x_host[layer][p][:T].numel() * 2 + y_host[layer][p][:T].numel() * 2
-        self.step(tok_dev[:T], max_mma_tiles, max_gather_tiles)
-        for layer in range(self.layers):
-            for p in range(len(self.projections)):
-                y_host[layer][p][:T].copy_(self.y[layer][p][:T], non_blocking=True)
-                d2h += y_host[layer][p][:T].numel() * 2
+            with torch.cuda.stream(s_in):
+                for p in range(n_proj):
+                    self.x[layer][p][:T].copy_(x_host[layer][p][:T], non_blocking=True)
+                    self.y[layer][p][:T].copy_(y_host[layer][p][:T], non_blocking=True)
+                    h2d += (x_host[layer][p][:T].numel() + y_host[layer][p][:T].numel()) * 2
+            if overlap:
+                cur.wait_stream(s_in)      # waits for what s_in holds now: this layer's inputs
+                self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles, phase_mask=flags,
+                              max_rank=max(self.ranks), first=layer * n_proj, count=n_proj)
+                s_out.wait_stream(cur)
+                with torch.cuda.stream(s_out):
+                    for p in range(n_proj):
+                        y_out_host[layer][p][:T].copy_(self.y[layer][p][:T], non_blocking=True)
+                        d2h += y_out_host[layer][p][:T].numel() * 2
+        if overlap:
+            cur.wait_stream(s_out)
+        else:
+            self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles, phase_mask=flags,
+                          max_rank=max(self.ranks))
+            for layer in range(self.layers):
+                for p in range(n_proj):
+                    y_out_host[layer][p][:T].copy_(self.y[layer][p][:T], non_blocking=True)
+                    d2h += y_out_host[layer][p][:T].numel() * 2
         return h2d, d2h

@@ -1,0 +1,144 @@
+"""Micro-benchmarks of the drop-in operator calls on one B200.
+
+    python -m valora_b200.microbench --config 1     # decode BGMV, bf16, 512 tokens
+
+Prints one JSON line.  A measurement walks `--layers` independent copies
+of the operator's tensors (own pools, own activations; together larger than
+L2), one shrink and one expand call per copy, and times the walk with CUDA
+events on the launching stream; GB/s are algorithmic bytes (activations once,
+every touched adapter row once, outputs read + written) over that time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import numpy as np
+import torch
+
+from . import ops, workloads
+from .pool import AdapterPool
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def _time_walk(fn, layers, reps, warmup):
+    """Median over reps of the device time of one walk over all layers, in ms.
+    The walk is captured once into a CUDA graph and replayed, so that what is
+    timed is the kernels back to back and not the host's call overhead."""
+    def walk():
+        for l in range(layers):
+            fn(l)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            walk()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        walk()
+    graph.replay()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return float(np.median(out))
+
+
+def bench_bgmv(layers: int, reps: int, warmup: int, dev):
+    """Config 1 through the 9-argument decode call: shrink (4096 -> 64) then expand
+    (64 -> 4096, punica weight layout), per token adapter index, no packing."""
+    b = workloads.config1()
+    H, r, n_ad, T = 4096, 64, b.n_adapters, b.T
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    pools_a = [AdapterPool(n_ad * r + 16, H, 1, b.dtype, dev, 1) for _ in range(layers)]
+    pools_b = [AdapterPool(n_ad * r + 16, H, 1, b.dtype, dev, 1) for _ in range(layers)]
+    for pools in (pools_a, pools_b):
+        for pool in pools:
+            for a in range(n_ad):
+                pool.load_adapter(f"a{a}", r, 0.25, [[None]])
+            pool.buffer[0].copy_((torch.randn(pool.buffer[0].shape, generator=g, device=dev) * 0.02).to(b.dtype))
+    x = [torch.randn(T, H, generator=g, device=dev).to(b.dtype) for _ in range(layers)]
+    y = [torch.randn(T, H, generator=g, device=dev).to(b.dtype) for _ in range(layers)]
+    v = [torch.zeros(T, r, dtype=b.dtype, device=dev) for _ in range(layers)]
+    idx = torch.from_numpy(b.tok_adapter.astype(np.int64)).to(dev)
+    pa0 = pools_a[0]
+    scales = pa0.a_scaling
+
+    def wview(pool):
+        return pool.buffer[0].view(pool.buffer[0].shape[0], 32, H // 32)
+
+    wa = [wview(p) for p in pools_a]
+    wb = [wview(p) for p in pools_b]
+
+    def shrink(l):
+        p = pools_a[l]
+        ops.bgmv(v[l], x[l], wa[l], p.a_start, p.a_len, p.a_loc, idx, 0, scales)
+
+    def expand(l):
+        p = pools_b[l]
+        ops.bgmv(y[l], v[l], wb[l], p.a_start, p.a_len, p.a_loc, idx, 0, scales)
+
+    touched = len(np.unique(b.tok_adapter))
+    e = 2
+    bytes_shrink = (T * H + touched * r * H + T * r) * e
+    bytes_expand = (T * r + touched * r * H + 2 * T * H) * e
+    ms_s = _time_walk(shrink, layers, reps, warmup)
+    ms_e = _time_walk(expand, layers, reps, warmup)
+    ms_b = _time_walk(lambda l: (shrink(l), expand(l)), layers, reps, warmup)
+    if ops.device_status() != 0:
+        raise SystemExit("a bounded wait gave up inside a kernel")
+    peak, src = _peak()
+
+    def gbs(nbytes, ms):
+        return nbytes * layers / (ms * 1e-3) / 1e9
+
+    return {
+        "bench": "decode_bgmv_dropin", "workload": b.name, "dtype": "bf16", "tokens": T, "adapters": n_ad,
+        "adapters_touched": touched, "rank": r, "hidden": H, "layers_walked": layers,
+        "bytes_resident": layers * (2 * (n_ad * r + 16) * H + 2 * T * H) * e,
+        "shrink": {"us_per_call": ms_s * 1e3 / layers, "gbs": gbs(bytes_shrink, ms_s),
+                   "frac": gbs(bytes_shrink, ms_s) / peak, "algorithmic_bytes": bytes_shrink},
+        "expand": {"us_per_call": ms_e * 1e3 / layers, "gbs": gbs(bytes_expand, ms_e),
+                   "frac": gbs(bytes_expand, ms_e) / peak, "algorithmic_bytes": bytes_expand},
+        "both": {"us_per_pair": ms_b * 1e3 / layers, "gbs": gbs(bytes_shrink + bytes_expand, ms_b),
+                 "frac": gbs(bytes_shrink + bytes_expand, ms_b) / peak,
+                 "tokens_per_s": T * layers / (ms_b * 1e-3)},
+        "peak_gbs": peak, "peak_source": src, "launch": "one CUDA graph per walk, replayed",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", type=int, default=1, choices=[1])
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device (there is no CPU fallback)")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    print(json.dumps(bench_bgmv(args.layers, args.reps, args.warmup, dev)))
+
+
+if __name__ == "__main__":
+    main()

@@ -319,15 +319,22 @@ class StepPlan:
         return self._ws
 
     def run(self, packed: Packed, scales: torch.Tensor, max_mma_tiles: int = 0,
-            max_gather_tiles: int = 0, phase_mask: int = PHASE_ALL, max_rank: int = 0):
-        """Enqueue shrink + expand of every problem for the packed batch."""
+            max_gather_tiles: int = 0, phase_mask: int = PHASE_ALL, max_rank: int = 0,
+            first: int = 0, count: Optional[int] = None):
+        """Enqueue shrink + expand for the packed batch: of every problem, or of
+        problems [first, first + count) (they share the front of the workspace, so
+        sub-ranges of one plan must run on one stream)."""
+        count = self.n - first if count is None else int(count)
+        if first < 0 or count < 1 or first + count > self.n:
+            raise RuntimeError("problem range outside the plan")
         _check_input(scales, "scales")
         if scales.dtype != self.dtype:
             raise RuntimeError("scales must have the plan's dtype")
         if packed.T > self.max_rows:
             raise RuntimeError("batch has more rows than the plan's buffers")
         ws = self.workspace(packed.T)
-        rc = self.lib.vlr_lora_step(_ptr(self.plan), self.n, packed.T, _ptr(packed.tiles),
+        plan_ptr = ctypes.c_void_p(self.plan.data_ptr() + first * (self.plan.numel() // self.n))
+        rc = self.lib.vlr_lora_step(plan_ptr, count, packed.T, _ptr(packed.tiles),
                                     _ptr(packed.gather_rows), int(max_mma_tiles),
                                     int(max_gather_tiles), _ptr(packed.counts), _ptr(scales),
                                     self.max_h_in, self.max_h_out, int(max_rank),
