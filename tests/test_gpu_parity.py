@@ -96,6 +96,39 @@ def test_bgmv_config1(ops):
     assert _err(y, truth) <= TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bgmv_many_tokens_mixed_ranks(ops, dtype):
+    """2500 tokens (three grouping windows), 37 adapters of ranks 8..128 including
+    ranks that are not powers of two, paged cells in random order, uneven adapter
+    popularity: every token still gets exactly its own adapter's update."""
+    H, N = 768, 2500
+    rng = np.random.default_rng(21)
+    ranks = rng.choice(np.array([8, 16, 24, 32, 40, 64, 128]), size=37)
+    A, B = rand_lora(ranks, H, H, dtype, n_slots=2, seed=8, wstd=0.05)
+    a_start, a_len, a_loc, total = build_tables(ranks, 2, shuffle=True, contiguous_slots=False, seed=4)
+    wa = fill_pool_a(A, ranks, a_start, a_loc, total, H, dtype)
+    wb = fill_pool_b(B, ranks, a_start, a_loc, total, H, dtype, layout="punica")
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(N, H, generator=g).to(dtype)
+    idx = torch.from_numpy(rng.choice(37, size=N, p=workloads.zipf_probs(37, 1.0))).long()
+    scales = (torch.rand(37, generator=g) + 0.5).to(dtype)
+    for qkvo in (0, 1):
+        v0 = torch.full((N, 128), 3.0).to(dtype)
+        ref_v = oracle.bgmv_shrink_ref(v0, x, wa, a_start, a_len, a_loc, idx, qkvo)
+        v = v0.to(DEV)
+        ops.bgmv(v, x.to(DEV), wa.view(total, 32, H // 32).to(DEV), t64(a_start, DEV), t64(a_len, DEV),
+                 t64(a_loc, DEV), idx.to(DEV), qkvo, scales.to(DEV))
+        assert _err(v, ref_v) <= TOL
+        y0 = torch.randn(N, H, generator=g).to(dtype)
+        vin = ref_v.to(dtype)
+        ref_y = oracle.bgmv_expand_ref(y0, vin, wb, a_start, a_len, a_loc, idx, qkvo, scales, layout="punica")
+        y = y0.to(DEV)
+        ops.bgmv(y, vin.to(DEV), wb.view(total, 32, H // 32).to(DEV), t64(a_start, DEV), t64(a_len, DEV),
+                 t64(a_loc, DEV), idx.to(DEV), qkvo, scales.to(DEV))
+        assert _err(y, ref_y) <= TOL
+    assert ops.device_status() == 0
+
+
 def test_bgmv_rejects_bad_arguments(ops):
     x = torch.zeros(4, 1024, dtype=torch.float16, device=DEV)
     y = torch.zeros(4, 16, dtype=torch.float16, device=DEV)

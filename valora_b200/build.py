@@ -8,7 +8,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libvlr.so")
-SOURCES = ["api.cu", "bgmv.cu", "pack.cu", "atmm_sm100.cu", "step.cu"]
+SOURCES = ["api.cu", "bgmv.cu", "bgmv_decode.cu", "pack.cu", "atmm_sm100.cu", "step.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

@@ -997,7 +997,9 @@ extern "C" int vlr_device_status(int reset) {
     int z = 0;
     cudaMemcpyToSymbol(vlr::g_status, &z, sizeof(int));
   }
-  return v;
+  const int d = vlr::bgmv_decode_status(reset);
+  if (d < 0) return -1;
+  return v | d;
 }
 
 // Debug aid: while a device buffer is set, CTA 0 of the tensor-core kernels writes
@@ -1006,5 +1008,6 @@ extern "C" int vlr_device_status(int reset) {
 extern "C" int vlr_debug_set_trace(void* dev_buffer, int64_t n_int64) {
   vlr::g_trace_ptr = reinterpret_cast<long long*>(dev_buffer);
   vlr::g_trace_cap = dev_buffer ? n_int64 : 0;
+  vlr::bgmv_decode_set_trace(vlr::g_trace_ptr, vlr::g_trace_cap);
   return VLR_OK;
 }

@@ -468,6 +468,11 @@ extern "C" int vlr_bgmv(void* y, const void* x, const void* w, const int64_t* a_
   if (expand && !lora_scales) return VLR_ERR_NULL;
   if (layout != VLR_LAYOUT_PUNICA && layout != VLR_LAYOUT_ROWS) return VLR_ERR_RANGE;
   if (!aligned16(x) || !aligned16(w) || (expand && !aligned16(y))) return VLR_ERR_ALIGN;
+  cudaStream_t s = (cudaStream_t)stream;
+  // adapter index per token: the ring kernels group the tokens by adapter themselves
+  if (!expand || layout == VLR_LAYOUT_PUNICA)
+    return bgmv_decode_launch(y, x, w, lora_scales, indicies, batch, a_start, a_len, a_loc, qkvo,
+                              (int)h_in, (int)h_out, dtype, s);
   BgmvGroups g{};
   g.indicies = indicies;
   g.batch = batch;
@@ -475,7 +480,6 @@ extern "C" int vlr_bgmv(void* y, const void* x, const void* w, const int64_t* a_
   g.a_len = a_len;
   g.a_loc = a_loc;
   g.qkvo = qkvo;
-  cudaStream_t s = (cudaStream_t)stream;
   if (dtype == VLR_F16)
     return launch_bgmv<__half, 8, 2>((__half*)y, (const __half*)x, (const __half*)w,
                                      (const __half*)lora_scales, g, batch, (int)h_in, (int)h_out,

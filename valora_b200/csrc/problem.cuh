@@ -105,6 +105,12 @@ int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, 
 int bgmv_gather_launch(void* y, const void* x, const void* w, const void* scales,
                        const BgmvGroups& groups, int64_t max_groups, int h_in, int h_out,
                        int layout, int dtype, cudaStream_t stream, int n_problems);
+int bgmv_decode_launch(void* y, const void* x, const void* w, const void* scales,
+                       const int64_t* indicies, int64_t batch, const int64_t* a_start,
+                       const int64_t* a_len, const int64_t* a_loc, int64_t qkvo, int h_in, int h_out,
+                       int dtype, cudaStream_t stream);
+int bgmv_decode_status(int reset);
+void bgmv_decode_set_trace(long long* dev_buffer, long long n);
 int atmm_launch(void* y, const void* x, const void* w, const void* scales, const TileSource& src,
                 int64_t max_tiles, int64_t T_rows, int h_in, int h_out, int64_t w_cells, int dtype,
                 int flags, cudaStream_t stream, int n_problems);

@@ -31,13 +31,26 @@ def _peak():
         return 6650.0, "fallback"
 
 
-def _time_walk(fn, layers, reps, warmup):
+def _time_walk(fn, layers, reps, warmup, eager=False):
     """Median over reps of the device time of one walk over all layers, in ms.
     The walk is captured once into a CUDA graph and replayed, so that what is
-    timed is the kernels back to back and not the host's call overhead."""
+    timed is the kernels back to back and not the host's call overhead
+    (eager=True launches call by call instead, for profilers)."""
     def walk():
         for l in range(layers):
             fn(l)
+
+    if eager:
+        out = []
+        for k in range(warmup + reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            walk()
+            e1.record()
+            torch.cuda.synchronize()
+            if k >= warmup:
+                out.append(e0.elapsed_time(e1))
+        return float(np.median(out))
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -62,7 +75,7 @@ def _time_walk(fn, layers, reps, warmup):
     return float(np.median(out))
 
 
-def bench_bgmv(layers: int, reps: int, warmup: int, dev):
+def bench_bgmv(layers: int, reps: int, warmup: int, dev, eager: bool = False):
     """Config 1 through the 9-argument decode call: shrink (4096 -> 64) then expand
     (64 -> 4096, punica weight layout), per token adapter index, no packing."""
     b = workloads.config1()
@@ -101,9 +114,9 @@ def bench_bgmv(layers: int, reps: int, warmup: int, dev):
     e = 2
     bytes_shrink = (T * H + touched * r * H + T * r) * e
     bytes_expand = (T * r + touched * r * H + 2 * T * H) * e
-    ms_s = _time_walk(shrink, layers, reps, warmup)
-    ms_e = _time_walk(expand, layers, reps, warmup)
-    ms_b = _time_walk(lambda l: (shrink(l), expand(l)), layers, reps, warmup)
+    ms_s = _time_walk(shrink, layers, reps, warmup, eager)
+    ms_e = _time_walk(expand, layers, reps, warmup, eager)
+    ms_b = _time_walk(lambda l: (shrink(l), expand(l)), layers, reps, warmup, eager)
     if ops.device_status() != 0:
         raise SystemExit("a bounded wait gave up inside a kernel")
     peak, src = _peak()
@@ -122,7 +135,7 @@ def bench_bgmv(layers: int, reps: int, warmup: int, dev):
         "both": {"us_per_pair": ms_b * 1e3 / layers, "gbs": gbs(bytes_shrink + bytes_expand, ms_b),
                  "frac": gbs(bytes_shrink + bytes_expand, ms_b) / peak,
                  "tokens_per_s": T * layers / (ms_b * 1e-3)},
-        "peak_gbs": peak, "peak_source": src, "launch": "one CUDA graph per walk, replayed",
+        "peak_gbs": peak, "peak_source": src, "launch": "call by call" if eager else "one CUDA graph per walk, replayed",
     }
 
 
@@ -132,12 +145,13 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--eager", action="store_true", help="launch call by call (no CUDA graph), for profilers")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    print(json.dumps(bench_bgmv(args.layers, args.reps, args.warmup, dev)))
+    print(json.dumps(bench_bgmv(args.layers, args.reps, args.warmup, dev, args.eager)))
 
 
 if __name__ == "__main__":
