@@ -59,6 +59,33 @@ def _serve(batch, world, rank):
     return s, y
 
 
+def _exchange_worker(rank, world, port, out_dir):
+    """Every rank holds an unsharded slice of the batch; rows go to their adapter's
+    owner, get the update there (oracle arithmetic), and come back in place."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        batch = _small_box_batch()
+        x, y0 = _activations(batch)
+        lo, hi = rank * batch.T // world, (rank + 1) * batch.T // world        # this rank's rows of the batch
+        tok = torch.from_numpy(batch.tok_adapter[lo:hi].astype(np.int64))
+        plan = shard.exchange_plan(tok.numpy(), world)
+        xr, ids, rc = shard.dispatch_rows(x[lo:hi], tok, plan)
+        yr, ids2, _ = shard.dispatch_rows(y0[lo:hi], tok, plan)
+        assert torch.equal(ids, ids2) and np.all(shard.owner(ids.numpy(), world) == rank)
+        out = yr.clone()
+        sc = batch.scalings()
+        for a in np.unique(ids.numpy()):                                       # rows of one adapter, one at a time
+            A, B = _weights(batch, int(a))
+            rows = torch.nonzero(ids == int(a)).flatten()
+            for r in rows.tolist():                                            # per-row: independent of how rows are grouped
+                out[r:r + 1] = oracle.ragged_lora_ref(yr[r:r + 1], xr[r:r + 1], [A], [B], [1], [0], [sc[a]])
+        back = shard.combine_rows(out, rc, plan)
+        np.save(os.path.join(out_dir, f"x{rank}.npy"), back.float().numpy())
+    finally:
+        dist.destroy_process_group()
+
+
 def _worker(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -121,3 +148,39 @@ def test_two_gloo_ranks_match_one_process(tmp_path):
                                   batch.req_adapter, batch.scalings())
     assert np.array_equal(got["full"], want.float().numpy())              # same rows, same arithmetic: bit-exact
     assert float(got["ms"]) == 11.0 and float(got["units"]) == float(batch.T)
+
+
+@pytest.mark.timeout(300)
+def test_rows_travel_to_their_adapters_owner_and_back(tmp_path):
+    world = 2
+    mp.spawn(_exchange_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    batch = _small_box_batch()
+    x, y0 = _activations(batch)
+    sc = batch.scalings()
+    want = y0.clone()
+    for t in range(batch.T):
+        a = int(batch.tok_adapter[t])
+        A, B = _weights(batch, a)
+        want[t:t + 1] = oracle.ragged_lora_ref(y0[t:t + 1], x[t:t + 1], [A], [B], [1], [0], [sc[a]])
+    got = np.concatenate([np.load(tmp_path / f"x{r}.npy") for r in range(world)])
+    assert np.array_equal(got, want.float().numpy())
+
+
+def test_replicating_hot_adapters_evens_the_load():
+    b = workloads.config4(tokens=4096, n_adapters=64)
+    counts = np.bincount(b.tok_adapter, minlength=64)
+    hot = shard.pick_replicated(counts, 4)
+    assert len(hot) == 4 and np.all(np.diff(hot) > 0) and counts[hot].min() >= np.sort(counts)[-4]
+    for world in (2, 4):
+        plain = [shard.route(b.req_adapter, b.req_len, world, r) for r in range(world)]
+        bal = [shard.route_with_replication(b.req_adapter, b.req_len, world, r, hot, 64) for r in range(world)]
+        shard.check_partition(bal, b.T)
+        assert max(s.T for s in bal) <= max(s.T for s in plain)
+        base = shard.replicated_base(64, world)
+        for s in bal:
+            glob_hot = s.tok_adapter >= base
+            # replicated adapters get the same local id on every GPU; partitioned ones keep a // world
+            assert np.array_equal(hot[s.tok_adapter[glob_hot] - base], b.tok_adapter[s.tok_index][glob_hot])
+            part = ~glob_hot
+            assert np.array_equal(shard.global_id(s.tok_adapter[part], world, s.rank), b.tok_adapter[s.tok_index][part])
+    assert len(shard.pick_replicated(counts, 0)) == 0
