@@ -192,9 +192,12 @@ __device__ __forceinline__ void trace_stamp(const TileSource& src, uint32_t k, i
 // shrink: persistent CTAs, 6-stage TMA ring over K, two accumulators in tensor
 // memory so the epilogue of one tile overlaps the main loop of the next.
 // ============================================================================
-// The operand ring is 192 KB; a stage is the X tile (16 KB) plus the weight rows
-// of the largest rank the launch may meet, so smaller ranks buy more stages
-// (rank 64: 8 stages of 24 KB, rank 128: 6 of 32 KB).  What bounds these kernels
+// The operand ring is 192 KB.  A K block of a full tile is the X tile (16 KB) plus
+// the adapter's rank rows (8 KB at rank 64, 16 KB at rank 128); a stage holds two of
+// them (4 stages of 48 KB when the launch cannot meet a rank above 64, else 3 of
+// 64 KB), shorter tiles up to four.  Stages of one K block each (8 x 24 KB) were 10 %
+// slower: per-stage costs (copy issue, barrier round trips) are paid per stage, and a
+// row's two 128-byte pieces are then requested together.  What bounds these kernels
 // is bytes in flight per SM against a memory latency of roughly 2 us under load.
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kShrinkMaxStages = 12;
@@ -231,7 +234,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
   if ((int64_t)blockIdx.x >= total) return;            // nothing for this CTA: no TMEM taken
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  constexpr int nst = NST;                             // 6 stages of 32 KB or 8 of 24 KB
+  constexpr int nst = NST;                             // 4 stages of 48 KB or 3 of 64 KB
   constexpr uint32_t stage_bytes = kRingBytes / NST;
   const uint32_t bars = base + kRingBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -868,7 +871,7 @@ static void size_rings(TileSource& src, int max_rank) {
   if (max_rank <= 0 || max_rank > kMaxRank) max_rank = kMaxRank;
   const int pad = (max_rank + 15) & ~15;
   src.max_rank = max_rank;
-  src.shrink_stages = pad <= 64 ? 8 : 6;               // 24 KB or 32 KB per stage
+  src.shrink_stages = pad <= 64 ? 4 : 3;               // 48 KB or 64 KB per stage: two K blocks of a full tile
   src.shrink_stage_bytes = kRingBytes / src.shrink_stages;
   src.exp_stages = pad <= 64 ? 4 : 3;                  // 48 KB or 64 KB per stage
   src.exp_stage_bytes = kRingBytes / src.exp_stages;
@@ -885,10 +888,10 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
       cudaError_t r = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
       if (e == cudaSuccess) e = r;
     };
-    set((const void*)atmm_shrink_kernel<__half, 6>, kShrinkSmem);
-    set((const void*)atmm_shrink_kernel<__half, 8>, kShrinkSmem);
-    set((const void*)atmm_shrink_kernel<__nv_bfloat16, 6>, kShrinkSmem);
-    set((const void*)atmm_shrink_kernel<__nv_bfloat16, 8>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__half, 3>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__half, 4>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__nv_bfloat16, 3>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__nv_bfloat16, 4>, kShrinkSmem);
     set((const void*)atmm_expand_kernel<__half, 3>, kExpSmem);
     set((const void*)atmm_expand_kernel<__half, 4>, kExpSmem);
     set((const void*)atmm_expand_kernel<__nv_bfloat16, 3>, kExpSmem);
@@ -918,11 +921,11 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
     const int64_t items = max_tiles * n_problems;
     const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
     const int acc = (flags & VLR_ATMM_ACCUMULATE_SHRINK) ? 1 : 0;
-    if (src.shrink_stages == 8)
-      atmm_shrink_kernel<T, 8><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
+    if (src.shrink_stages == 4)
+      atmm_shrink_kernel<T, 4><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
                                                                         h_in, h_out, acc);
     else
-      atmm_shrink_kernel<T, 6><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
+      atmm_shrink_kernel<T, 3><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
                                                                         h_in, h_out, acc);
   } else {
     if (!step && (rc = make_map_set(&maps, y, T_rows, w, w_cells, h_out, dtype)) != VLR_OK) return rc;
