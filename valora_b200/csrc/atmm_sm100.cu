@@ -773,27 +773,42 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(ab));
+        // phase 2: 4 rows x 128 bytes per instruction, rows of this segment only.  The stage
+        // is handed back as soon as its bytes are in registers; the second half of the global
+        // stores (which the SM's store path throttles) drains afterwards.  (Two alternatives
+        // measured slower on the mixed step: a tensor store of whole 32-row blocks - the copy
+        // engine reads the tile only after the loads queued ahead of it, and the stage cannot
+        // be reused before that - and handing phase 2 to one, two or four dedicated store
+        // warps, +3 %, with more than 12 warps also costing registers.)
+        const int ch = lane & 7;
+        const int col = n0 + j * kBoxCols + ch * 8;
+        uint4 ov[4];
         if (warp_live) {
-          // phase 2: 4 rows x 128 bytes per instruction, rows of this segment only
-          const int ch = lane & 7;
-          const int col = n0 + j * kBoxCols + ch * 8;
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint4 ov[4];
+          for (int p = 0; p < 4; ++p) {
+            const int rr = q * 32 + p * 4 + (lane >> 3);
+            ov[p] = lds128(blk + rr * 128 + ((ch ^ (rr & 7)) << 4));
+          }
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              const int rr = q * 32 + (half * 4 + p) * 4 + (lane >> 3);
-              ov[p] = lds128(blk + rr * 128 + ((ch ^ (rr & 7)) << 4));
-            }
+          for (int p = 0; p < 4; ++p) {
+            const int rr = q * 32 + p * 4 + (lane >> 3);
+            if (rr < ti.rows && col < h_out) stg128(y + (int64_t)(ti.row0 + rr) * h_out + col, ov[p]);
+          }
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              const int rr = q * 32 + (half * 4 + p) * 4 + (lane >> 3);
-              if (rr < ti.rows && col < h_out) stg128(y + (int64_t)(ti.row0 + rr) * h_out + col, ov[p]);
-            }
+          for (int p = 0; p < 4; ++p) {
+            const int rr = q * 32 + (4 + p) * 4 + (lane >> 3);
+            ov[p] = lds128(blk + rr * 128 + ((ch ^ (rr & 7)) << 4));
           }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(s));
+        if (warp_live) {
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const int rr = q * 32 + (4 + p) * 4 + (lane >> 3);
+            if (rr < ti.rows && col < h_out) stg128(y + (int64_t)(ti.row0 + rr) * h_out + col, ov[p]);
+          }
+        }
         if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 3);
       }
       ++li;
