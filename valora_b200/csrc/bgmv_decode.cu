@@ -279,19 +279,28 @@ __device__ __forceinline__ void halve(float (&v)[kShrSlice * kG], int lane, int 
 // stale bytes; their sums are never stored.
 template <typename T, int NG>
 __device__ __forceinline__ void shrink_piece(uint32_t xaddr, uint32_t waddr, int nlive,
-                                             float (&acc)[kShrSlice * kG]) {
-  float xf[NG][8];
+                                             float2 (&acc)[kShrSlice][kG / 2]) {
+  // tokens in pairs: one packed fp32 multiply-add (fma.rn.f32x2) serves two tokens
+  float2 xf[NG / 2][8];
 #pragma unroll
-  for (int g = 0; g < NG; ++g) unpack8<T>(lds128(xaddr + g * kShrRowBytes), xf[g]);
+  for (int h = 0; h < NG / 2; ++h) {
+    float a[8], b[8];
+    unpack8<T>(lds128(xaddr + (2 * h) * kShrRowBytes), a);
+    unpack8<T>(lds128(xaddr + (2 * h + 1) * kShrRowBytes), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xf[h][e] = make_float2(a[e], b[e]);
+  }
 #pragma unroll
   for (int j = 0; j < kShrSlice; ++j) {
     if (j < nlive) {
       float wf[8];
       unpack8<T>(lds128(waddr + j * kShrRowBytes), wf);
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
+      for (int e = 0; e < 8; ++e) {
+        const float2 w2 = make_float2(wf[e], wf[e]);
 #pragma unroll
-        for (int g = 0; g < NG; ++g) acc[j * kG + g] = fmaf(wf[e], xf[g][e], acc[j * kG + g]);
+        for (int h = 0; h < NG / 2; ++h) acc[j][h] = __ffma2_rn(w2, xf[h][e], acc[j][h]);
+      }
     }
   }
 }
@@ -399,7 +408,7 @@ bgmv_decode_shrink_kernel(T* __restrict__ v, const T* __restrict__ x, const T* _
       // -------------------------------------------------------------- consumers
       const int cw = warp - kProducers;
       const int piece = (cw * 32 + lane) * 16;          // this lane's bytes of every row of a stage
-      float acc[kShrSlice * kG];
+      float2 acc[kShrSlice][kG / 2];                      // [rank row][token pair]
       int rb = 0;
       while (true) {
         const int s = it % kShrStages;
@@ -412,7 +421,9 @@ bgmv_decode_shrink_kernel(T* __restrict__ v, const T* __restrict__ x, const T* _
         if (valid) {
           if (in.first) {
 #pragma unroll
-            for (int i = 0; i < kShrSlice * kG; ++i) acc[i] = 0.f;
+            for (int j = 0; j < kShrSlice; ++j)
+#pragma unroll
+              for (int h = 0; h < kG / 2; ++h) acc[j][h] = make_float2(0.f, 0.f);
           }
           if (piece < in.cb) {
             const uint32_t xa = stage(s) + piece, wa = xa + kG * kShrRowBytes;
@@ -421,15 +432,23 @@ bgmv_decode_shrink_kernel(T* __restrict__ v, const T* __restrict__ x, const T* _
           }
           if (in.last) {
             // 64 partial sums per lane -> 2 per lane -> per-warp rows in shared memory
-            halve<64>(acc, lane, 16);
-            halve<32>(acc, lane, 8);
-            halve<16>(acc, lane, 4);
-            halve<8>(acc, lane, 2);
-            halve<4>(acc, lane, 1);
+            float fl[kShrSlice * kG];                    // [rank row * 8 + token]
+#pragma unroll
+            for (int j = 0; j < kShrSlice; ++j)
+#pragma unroll
+              for (int h = 0; h < kG / 2; ++h) {
+                fl[j * kG + 2 * h] = acc[j][h].x;
+                fl[j * kG + 2 * h + 1] = acc[j][h].y;
+              }
+            halve<64>(fl, lane, 16);
+            halve<32>(fl, lane, 8);
+            halve<16>(fl, lane, 4);
+            halve<8>(fl, lane, 2);
+            halve<4>(fl, lane, 1);
             const int idx = ((lane & 16) ? 32 : 0) + ((lane & 8) ? 16 : 0) + ((lane & 4) ? 8 : 0) +
                             ((lane & 2) ? 4 : 0) + ((lane & 1) ? 2 : 0);
-            redw[rb][cw][idx] = acc[0];
-            redw[rb][cw][idx + 1] = acc[1];
+            redw[rb][cw][idx] = fl[0];
+            redw[rb][cw][idx + 1] = fl[1];
             consumer_barrier();
             const int ct = cw * 32 + lane;              // 0..255
             if (ct < kShrSlice * kG) {
@@ -584,7 +603,7 @@ __device__ __forceinline__ void flush_y(PendingY<T>& p, const float* __restrict_
 // the scaled sums of every (token, column) go to the warp's tile.
 template <typename T, int CPO, int NG>
 __device__ __forceinline__ void expand_stage(const ExpandInfo& in, uint32_t st, float* __restrict__ tile,
-                                             int cw, int lane, const float (&vs)[kG][8]) {
+                                             int cw, int lane, const float2 (&vs)[kG / 2][8]) {
   constexpr int opw = 32 / CPO;                        // columns per warp instruction
   constexpr int cps = (1024 / CPO) < kExpMaxCps ? (1024 / CPO) : kExpMaxCps;
   constexpr int cols_w = cps / kConsumers;             // 64, 64, 32, 16, 8
@@ -595,15 +614,23 @@ __device__ __forceinline__ void expand_stage(const ExpandInfo& in, uint32_t st, 
 #pragma unroll
   for (int rd = 0; rd < rounds; ++rd) {
     const int col = cw * cols_w + rd * opw + ol;
+    float2 p2[kG / 2];
 #pragma unroll
-    for (int g = 0; g < kG; ++g) part[rd][g] = 0.f;
+    for (int h = 0; h < kG / 2; ++h) p2[h] = make_float2(0.f, 0.f);
     float wf[8];
     unpack8<T>(col < ncol && kc * 8 < rank ? lds128(st + (uint32_t)(col * rank + kc * 8) * 2)
                                             : make_uint4(0, 0, 0, 0), wf);
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
+    for (int e = 0; e < 8; ++e) {
+      const float2 w2 = make_float2(wf[e], wf[e]);
 #pragma unroll
-      for (int g = 0; g < NG; ++g) part[rd][g] = fmaf(vs[g][e], wf[e], part[rd][g]);
+      for (int h = 0; h < NG / 2; ++h) p2[h] = __ffma2_rn(vs[h][e], w2, p2[h]);
+    }
+#pragma unroll
+    for (int h = 0; h < kG / 2; ++h) {
+      part[rd][2 * h] = p2[h].x;
+      part[rd][2 * h + 1] = p2[h].y;
+    }
   }
   const int g0 = reduce_scatter<CPO, rounds>(part, lane);
   constexpr int nval = CPO >= 8 ? 1 : kG / CPO;
@@ -740,7 +767,7 @@ bgmv_decode_expand_kernel(T* __restrict__ y, const T* __restrict__ v, const T* _
     } else {
       // -------------------------------------------------------------- consumers
       const int cw = warp - kProducers;
-      float vs[kG][8];
+      float2 vs[kG / 2][8];                              // [token pair][element]: packed for fma.rn.f32x2
       PendingY<T> pend;
       pend.yp[0] = pend.yp[1] = nullptr;
       int buf = 0;
@@ -759,13 +786,18 @@ bgmv_decode_expand_kernel(T* __restrict__ y, const T* __restrict__ v, const T* _
             const int kc = lane % cpo;
             const float scale = in.scale;
 #pragma unroll
-            for (int g = 0; g < kG; ++g) {
-              uint4 raw = make_uint4(0, 0, 0, 0);
-              if (g < in.nrows && kc * 8 < in.vk)
-                raw = lds128(stage(s) + kExpWBytes + g * (kMaxRank * 2) + kc * 16);
-              unpack8<T>(raw, vs[g]);
+            for (int h = 0; h < kG / 2; ++h) {
+              float a[8], b[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) vs[g][e] *= scale;
+              for (int u = 0; u < 2; ++u) {
+                const int g = 2 * h + u;
+                uint4 raw = make_uint4(0, 0, 0, 0);
+                if (g < in.nrows && kc * 8 < in.vk)
+                  raw = lds128(stage(s) + kExpWBytes + g * (kMaxRank * 2) + kc * 16);
+                unpack8<T>(raw, u == 0 ? a : b);
+              }
+#pragma unroll
+              for (int e = 0; e < 8; ++e) vs[h][e] = make_float2(a[e] * scale, b[e] * scale);
             }
           }
           PendingY<T> cur;
