@@ -463,8 +463,46 @@ def test_step_from_host_buffers_matches_resident_step(ops, overlap):
     assert h2d == b.T * 8 + L * b.T * (512 + 512 + 512 + 1024) * 2 and d2h == L * b.T * (512 + 1024) * 2
 
 
+@pytest.mark.parametrize("gather_path", ["mma", "simt"])
+def test_step_narrow_projections(ops, gather_path):
+    """projections narrower than the 128-wide rank buffer (64 -> 64, 64 -> 192, 128 -> 64):
+    the step must still run shrink as shrink and expand as expand"""
+    b = workloads.config0()
+    b.projections = [("a", 64, 64), ("b", 64, 192), ("c", 128, 64)]
+    _step_case(ops, b, [0, 1, 2], layers=2, gather_path=gather_path)
+
+
 def test_step_gathered_rows_mixed_ranks(ops):
     """config 4 slice: 1024 adapters of ranks 16..128, mostly decode rows, many adapters
     with a handful of rows each - gathered tiles of every rank on the tensor cores"""
     b = workloads.config4(n_gpus=8, rank=3)
     _step_case(ops, b, [0])
+
+
+# --------------------------------------------------------------------------- merged mode
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_merge_and_unmerge_adapter(ops, dtype):
+    """W +- scaling * A @ B on the expand kernel (rows of W as tokens), against fp32 torch;
+    merge followed by unmerge returns W up to the two roundings."""
+    from valora_b200 import merge
+    from valora_b200.pool import AdapterPool
+    h_in, h_out, ranks = 1024, 1536, [16, 64, 24]
+    pa = AdapterPool(sum(ranks) * 2 + 16, h_in, 2, dtype, DEV, 1)
+    pb = AdapterPool(sum(ranks) * 2 + 16, h_out, 2, dtype, DEV, 1)
+    g = torch.Generator().manual_seed(4)
+    A, B = {}, {}
+    for a, r in enumerate(ranks):
+        A[a] = [(torch.randn(r, h_in, generator=g) * 0.05).to(dtype) for _ in range(2)]     # A^T rows per slot
+        B[a] = [(torch.randn(r, h_out, generator=g) * 0.05).to(dtype) for _ in range(2)]
+        pa.load_adapter(f"a{a}", r, 16.0 / r, [[A[a][0], A[a][1]]])
+        pb.load_adapter(f"a{a}", r, 16.0 / r, [[B[a][0], B[a][1]]])
+    W0 = torch.randn(h_in, h_out, generator=g).to(dtype)
+    for adapter, slot in ((1, 0), (2, 1), (0, 1)):
+        W = W0.to(DEV)
+        merge.merge_adapter(W, pa, pb, 0, slot, slot, adapter)
+        s = float(torch.tensor(16.0 / ranks[adapter]).to(dtype))
+        want = W0.float() + s * (A[adapter][slot].float().t() @ B[adapter][slot].float())
+        assert _err(W, want) <= TOL
+        merge.unmerge_adapter(W, pa, pb, 0, slot, slot, adapter)
+        assert float((W.float().cpu() - W0.float()).abs().max()) <= 4e-2                      # two roundings of |w| < 8
+    assert ops.device_status() == 0

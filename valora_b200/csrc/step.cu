@@ -92,22 +92,27 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   g.vstride = T * kMaxRank;
 
   int rc = VLR_OK;
-  // shrink: h_in >= h_out selects it in the launchers
+  // The launchers pick the direction from h_in >= h_out, and in step mode use the two
+  // widths only to size grids (every problem brings its own).  Plans whose widest
+  // projection is narrower than the rank buffer must still go the right way.
+  const int shrink_h_in = (int)max_h_in > kMaxRank ? (int)max_h_in : kMaxRank;
+  const int expand_h_out = (int)max_h_out > kMaxRank ? (int)max_h_out : kMaxRank + 8;
+  // shrink
   if (phase_mask & VLR_PHASE_SHRINK_MMA)
-    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, max_h_in, kMaxRank, 0,
+    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, shrink_h_in, kMaxRank, 0,
                      dtype, 0, s, n_problems);
   if (rc != VLR_OK) return rc;
   if (phase_mask & VLR_PHASE_SHRINK_GATHER)
-    rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, max_h_in,
+    rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, shrink_h_in,
                             kMaxRank, VLR_LAYOUT_ROWS, dtype, s, n_problems);
   if (rc != VLR_OK) return rc;
   // expand
   if (phase_mask & VLR_PHASE_EXPAND_MMA)
-    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, kMaxRank, max_h_out, 0,
+    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, kMaxRank, expand_h_out, 0,
                      dtype, VLR_ATMM_APPLY_SCALE, s, n_problems);
   if (rc != VLR_OK) return rc;
   if (phase_mask & VLR_PHASE_EXPAND_GATHER)
     rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, kMaxRank,
-                            max_h_out, VLR_LAYOUT_ROWS, dtype, s, n_problems);
+                            expand_h_out, VLR_LAYOUT_ROWS, dtype, s, n_problems);
   return rc;
 }
