@@ -37,7 +37,8 @@ constexpr int kTileM = 128;
 constexpr int kShrinkProducers = 3;                    // warps 0..2, MMA = warp 3, epilogue = 4..7
 constexpr int kShrinkMmaWarp = kShrinkProducers;
 constexpr int kShrinkEpiWarp0 = 4;
-constexpr int kThreads = 32 * (kShrinkEpiWarp0 + 4);
+constexpr int kShrinkFetchWarp = kShrinkEpiWarp0 + 4;   // warp 8: draws work items
+constexpr int kThreads = 32 * (kShrinkFetchWarp + 1);
 constexpr int kBoxRowsW = 16;        // weight rows per TMA box
 constexpr int kBoxCols = 64;         // 64 two-byte elements = 128 bytes = swizzle span
 constexpr int kGatherRows = 16;      // rows of a gather tile (row slots 0, 8, ..., 120)
@@ -180,6 +181,49 @@ __device__ __forceinline__ int64_t total_items(const TileSource& src) {
   return src.max_tiles * src.nsplit;
 }
 
+
+// ---- which items a CTA works on
+// With a device counter the CTAs draw items as they go (the first one is blockIdx.x, the
+// k-th draw yields gridDim.x + k), which evens out tiles of very different sizes; without
+// one, item k of a CTA is blockIdx.x + k * gridDim.x.  All roles of a CTA must see the same
+// sequence: one fetch thread publishes it through a small ring in shared memory (a full
+// and an empty mbarrier per slot), every other warp reads it in order.  -1 ends the sequence.
+constexpr int kItemRing = 3;
+struct ItemFeed {
+  uint32_t full0, empty0, ring0;                       // shared-memory addresses
+};
+__device__ __forceinline__ int64_t next_item(const TileSource& src, const ItemFeed& f, uint32_t k,
+                                             int64_t total, volatile int* abort_flag) {
+  if (src.item_counter == nullptr) {
+    const int64_t it = (int64_t)blockIdx.x + (int64_t)k * gridDim.x;
+    return it < total ? it : -1;
+  }
+  long long item = -1;
+  if ((threadIdx.x & 31) == 0) {
+    const uint32_t s = k % kItemRing;
+    if (mbar_wait(f.full0 + 8u * s, (k / kItemRing) & 1, abort_flag)) {
+      asm volatile("ld.shared.s64 %0, [%1];" : "=l"(item) : "r"(f.ring0 + 8u * s));
+      mbar_arrive(f.empty0 + 8u * s);
+    }
+  }
+  return __shfl_sync(0xffffffffu, item, 0);
+}
+// The fetch thread's loop (one lane of a warp that has nothing else to do).
+__device__ __forceinline__ void feed_items(const TileSource& src, const ItemFeed& f, int64_t total,
+                                           volatile int* abort_flag) {
+  if (src.item_counter == nullptr) return;
+  for (uint32_t k = 0;; ++k) {
+    const uint32_t s = k % kItemRing;
+    if (!mbar_wait(f.empty0 + 8u * s, ((k / kItemRing) & 1) ^ 1, abort_flag)) return;
+    long long item = k == 0 ? (long long)blockIdx.x
+                            : (long long)gridDim.x + (long long)atomicAdd(src.item_counter, 1u);
+    if (item >= total) item = -1;
+    asm volatile("st.shared.s64 [%0], %1;" ::"r"(f.ring0 + 8u * s), "l"(item) : "memory");
+    mbar_arrive(f.full0 + 8u * s);
+    if (item < 0) return;
+  }
+}
+
 __device__ int g_status;             // 0 ok, 1 a bounded wait gave up
 
 // Debug aid: CTA 0 stamps clock64 into src.trace, slot `what` of stage `k`.
@@ -241,6 +285,10 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
   auto empty_bar = [&](int s) { return bars + 8u * (kShrinkMaxStages + s); };
   auto tfull_bar = [&](int ab) { return bars + 8u * (2 * kShrinkMaxStages + ab); };
   auto tempty_bar = [&](int ab) { return bars + 8u * (2 * kShrinkMaxStages + 2 + ab); };
+  ItemFeed feed;
+  feed.full0 = bars + 8u * (2 * kShrinkMaxStages + 4);
+  feed.empty0 = feed.full0 + 8u * kItemRing;
+  feed.ring0 = bars + 384u;
   auto x_stage = [&](int s) { return base + (uint32_t)s * stage_bytes; };
 
   if (threadIdx.x == 0) {
@@ -252,6 +300,10 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     for (int ab = 0; ab < 2; ++ab) {
       mbar_init(tfull_bar(ab), 1);
       mbar_init(tempty_bar(ab), 4);
+    }
+    for (int i = 0; i < kItemRing; ++i) {
+      mbar_init(feed.full0 + 8u * i, 1);
+      mbar_init(feed.empty0 + 8u * i, kShrinkFetchWarp);   // every other warp reads every item
     }
     fence_barrier_init();
   }
@@ -279,7 +331,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     // 128-byte swizzle from the address bits, so the slots form a dense tile.
     uint32_t kiter = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
+    for (uint32_t ik = 0; ok; ++ik) {
+      const int64_t item = next_item(src, feed, ik, total, &abort_s);
+      if (item < 0) break;
       const TileInfo ti = get_tile(src, item, false);
       if (!ti.valid) continue;
       const MapSet* ms = src.plan ? &src.plan[ti.problem].shrink : &maps_;
@@ -337,7 +391,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     // ------------------------------------------------------------ MMA issuer
     uint32_t kiter = 0, li = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
+    for (uint32_t ik = 0; ok; ++ik) {
+      const int64_t item = next_item(src, feed, ik, total, &abort_s);
+      if (item < 0) break;
       const TileInfo ti = get_tile(src, item, false);
       if (!ti.valid) continue;
       if (lane == 0) {
@@ -376,12 +432,14 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
     }
-  } else {
+  } else if (warp < kShrinkFetchWarp) {
     // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
     const int row = q * 32 + lane;
     uint32_t li = 0;
-    for (int64_t item = blockIdx.x; item < total; item += gridDim.x) {
+    for (uint32_t ik = 0;; ++ik) {
+      const int64_t item = next_item(src, feed, ik, total, &abort_s);
+      if (item < 0) break;
       const TileInfo ti = get_tile(src, item, false);
       if (!ti.valid) continue;
       const int ab = li & 1;
@@ -437,6 +495,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       ++li;
     }
     tc_fence_before();
+  } else {
+    // ------------------------------------------------------------ work items
+    if (lane == 0) feed_items(src, feed, total, &abort_s);
   }
   __syncthreads();
   if (warp == kShrinkMmaWarp) {
@@ -456,7 +517,8 @@ constexpr int kExpEpiWarp0 = 0;                        // epilogue = warps 0..7
 constexpr int kExpProducers = 2;                       // producers = warps 8..9
 constexpr int kExpProdWarp0 = kExpEpiWarps;
 constexpr int kExpMmaWarp = kExpProdWarp0 + kExpProducers;   // warp 18
-constexpr int kExpThreads = 32 * (kExpMmaWarp + 1);
+constexpr int kExpFetchWarp = kExpMmaWarp + 1;           // warp 11: draws work items
+constexpr int kExpThreads = 32 * (kExpFetchWarp + 1);
 constexpr int kExpTileN = 128;
 constexpr int kExpABytes = 2 * kTileM * 128;           // V tile, two 64-column K blocks: 32 KB
 // A stage holds the B rows of its columns (64-column blocks k_pad * 128 bytes apart)
@@ -511,6 +573,10 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
   auto tempty_bar = [&](int ab) { return bars + 8u * (2 * kExpMaxStages + kExpAccBufs + ab); };
   const uint32_t a_ready_bar = bars + 8u * (2 * kExpMaxStages + 2 * kExpAccBufs);
   const uint32_t a_free_bar = bars + 8u * (2 * kExpMaxStages + 2 * kExpAccBufs + 1);
+  ItemFeed feed;
+  feed.full0 = bars + 8u * (2 * kExpMaxStages + 2 * kExpAccBufs + 2);
+  feed.empty0 = feed.full0 + 8u * kItemRing;
+  feed.ring0 = bars + 384u;
 
   if (threadIdx.x == 0) {
     abort_s = 0;
@@ -524,6 +590,10 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     }
     mbar_init(a_ready_bar, 32 * kExpEpiWarps);
     mbar_init(a_free_bar, 1);
+    for (int i = 0; i < kItemRing; ++i) {
+      mbar_init(feed.full0 + 8u * i, 1);
+      mbar_init(feed.empty0 + 8u * i, kExpFetchWarp);      // every other warp reads every item
+    }
     fence_barrier_init();
   }
   if (warp == kExpMmaWarp) {
@@ -543,7 +613,9 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     // 64-column block (read back by the epilogue only, so no swizzle).
     uint32_t it = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
+    for (uint32_t ik = 0; ok; ++ik) {
+      const int64_t item = next_item(src, feed, ik, total, &abort_s);
+      if (item < 0) break;
       const TileInfo ti = get_tile(src, item, true);
       if (!ti.valid) continue;
       const ExpRange er = exp_range(src, ti, h_out_);
@@ -597,7 +669,9 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     // ------------------------------------------------------------ MMA issuer
     uint32_t it = 0, li = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
+    for (uint32_t ik = 0; ok; ++ik) {
+      const int64_t item = next_item(src, feed, ik, total, &abort_s);
+      if (item < 0) break;
       const TileInfo ti = get_tile(src, item, true);
       if (!ti.valid) continue;
       const ExpRange er = exp_range(src, ti, h_out_);
@@ -666,7 +740,9 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     const int et = threadIdx.x - 32 * kExpEpiWarp0;    // 0..255
     uint32_t it = 0, li = 0;
     bool ok = true;
-    for (int64_t item = blockIdx.x; item < total && ok; item += gridDim.x) {
+    for (uint32_t ik = 0; ok; ++ik) {
+      const int64_t item = next_item(src, feed, ik, total, &abort_s);
+      if (item < 0) break;
       const TileInfo ti = get_tile(src, item, true);
       if (!ti.valid) continue;
       const ExpRange er = exp_range(src, ti, h_out_);
@@ -814,6 +890,9 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       ++li;
     }
     tc_fence_before();
+  } else if (warp == kExpFetchWarp) {
+    // ------------------------------------------------------------ work items
+    if (lane == 0) feed_items(src, feed, total, &abort_s);
   }
   __syncthreads();
   if (warp == kExpMmaWarp) {

@@ -86,6 +86,9 @@ struct TileSource {
   // optional timing trace of CTA 0 (clock64 stamps, 4 per pipeline stage); null = off
   long long* trace;
   int64_t trace_cap;
+  // work distribution: null = item k of a CTA is blockIdx.x + k * gridDim.x; else a
+  // zeroed device counter from which the CTAs draw their next item (after the first)
+  unsigned int* item_counter;
   // work decomposition, filled by the launcher
   int64_t max_tiles;                 // mode 0: upper bound of the tile count
   int n_problems;

@@ -45,7 +45,7 @@ extern "C" int vlr_step_plan_build(const vlr_problem_t* problems, int n_problems
 
 extern "C" size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems) {
   if (T <= 0 || n_problems <= 0) return 256;
-  return (size_t)n_problems * (size_t)T * kMaxRank * 2 + 256;
+  return (size_t)n_problems * (size_t)T * kMaxRank * 2 + 256 + 512;   // V buffers, alignment, work-item counters
 }
 
 extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
@@ -61,7 +61,9 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   if ((reinterpret_cast<uintptr_t>(plan_dev) & 127u) != 0) return VLR_ERR_ALIGN;
   char* vb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
   const size_t need = (size_t)n_problems * (size_t)T * kMaxRank * 2;
-  if ((size_t)(vb - reinterpret_cast<char*>(workspace)) + need > workspace_bytes) return VLR_ERR_WORKSPACE;
+  const size_t need_all = ((need + 255) & ~size_t(255)) + 256;     // + two work-item counters, 128 bytes apart
+  if ((size_t)(vb - reinterpret_cast<char*>(workspace)) + need_all > workspace_bytes) return VLR_ERR_WORKSPACE;
+  unsigned int* counters = reinterpret_cast<unsigned int*>(vb + ((need + 255) & ~size_t(255)));
   // every tile holds at least one row
   if (max_mma_tiles <= 0 || max_mma_tiles > T) max_mma_tiles = T;
   if (max_gather_tiles <= 0 || max_gather_tiles > T) max_gather_tiles = T;
@@ -92,12 +94,16 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   g.vstride = T * kMaxRank;
 
   int rc = VLR_OK;
+  // the tensor-core kernels draw their work items from these (tiles differ a lot in size)
+  cudaError_t ce = cudaMemsetAsync(counters, 0, 256, s);
+  if (ce != cudaSuccess) return (int)ce;
   // The launchers pick the direction from h_in >= h_out, and in step mode use the two
   // widths only to size grids (every problem brings its own).  Plans whose widest
   // projection is narrower than the rank buffer must still go the right way.
   const int shrink_h_in = (int)max_h_in > kMaxRank ? (int)max_h_in : kMaxRank;
   const int expand_h_out = (int)max_h_out > kMaxRank ? (int)max_h_out : kMaxRank + 8;
   // shrink
+  src.item_counter = counters;
   if (phase_mask & VLR_PHASE_SHRINK_MMA)
     rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, shrink_h_in, kMaxRank, 0,
                      dtype, 0, s, n_problems);
@@ -107,6 +113,7 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
                             kMaxRank, VLR_LAYOUT_ROWS, dtype, s, n_problems);
   if (rc != VLR_OK) return rc;
   // expand
+  src.item_counter = counters + 32;
   if (phase_mask & VLR_PHASE_EXPAND_MMA)
     rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, kMaxRank, expand_h_out, 0,
                      dtype, VLR_ATMM_APPLY_SCALE, s, n_problems);
