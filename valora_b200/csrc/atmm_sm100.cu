@@ -188,7 +188,7 @@ __device__ __forceinline__ int64_t total_items(const TileSource& src) {
 // one, item k of a CTA is blockIdx.x + k * gridDim.x.  All roles of a CTA must see the same
 // sequence: one fetch thread publishes it through a small ring in shared memory (a full
 // and an empty mbarrier per slot), every other warp reads it in order.  -1 ends the sequence.
-constexpr int kItemRing = 3;
+constexpr int kItemRing = 2;
 struct ItemFeed {
   uint32_t full0, empty0, ring0;                       // shared-memory addresses
 };
