@@ -137,20 +137,27 @@ __device__ void build_groups(const int64_t* __restrict__ indicies, int64_t w0, i
     for (int c = 0; c < 4; ++c) {
       const int t = warp * 128 + c * 32 + lane;
       const int a = ids[t];
-      // lanes holding the same adapter id (32 broadcasts; cheaper here than match.any)
+      // lanes holding the same adapter id: every lane reads the chunk's 32 ids (eight
+      // broadcast 16-byte loads; 32 shuffles or match.any cost several times more here)
       unsigned peers = 0;
+      const int4* chunk = reinterpret_cast<const int4*>(ids + warp * 128 + c * 32);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) peers |= (__shfl_sync(0xffffffffu, a, i) == a ? 1u : 0u) << i;
-      if (a >= 0) {
-        const int leader = __ffs(peers) - 1;
-        int before = 0;
-        if (lane == leader) {
-          before = cntr[warp * kBins + a];
-          cntr[warp * kBins + a] = (uint16_t)(before + __popc(peers));
-        }
-        before = __shfl_sync(peers, before, leader);
-        trank[t] = (int16_t)(before + __popc(peers & ((1u << lane) - 1u)));
+      for (int i = 0; i < 8; ++i) {
+        const int4 v = chunk[i];
+        peers |= (v.x == a ? 1u : 0u) << (4 * i) | (v.y == a ? 1u : 0u) << (4 * i + 1) |
+                 (v.z == a ? 1u : 0u) << (4 * i + 2) | (v.w == a ? 1u : 0u) << (4 * i + 3);
       }
+      // the lowest peer reads and bumps the running count; everybody fetches it from there
+      // (one full-mask shuffle with a per-lane source: a shuffle per peer group would be
+      // issued once per distinct mask)
+      const int leader = __ffs(peers) - 1;
+      int before = 0;
+      if (a >= 0 && lane == leader) {
+        before = cntr[warp * kBins + a];
+        cntr[warp * kBins + a] = (uint16_t)(before + __popc(peers));
+      }
+      before = __shfl_sync(0xffffffffu, before, leader);
+      if (a >= 0) trank[t] = (int16_t)(before + __popc(peers & ((1u << lane) - 1u)));
       __syncwarp();
     }
   }
