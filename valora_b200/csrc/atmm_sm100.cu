@@ -65,11 +65,6 @@ struct TileInfo {
   int64_t wrow0;     // first pool cell of the slot
 };
 
-// row r of a tile -> row of the caller's x / y / v
-__device__ __forceinline__ int tile_row(const TileSource& src, const TileInfo& ti, int r) {
-  return ti.gather ? src.gather_rows[ti.row0 + r] : ti.row0 + r;
-}
-
 // Consecutive activation rows [row0, row0 + rows) as one to two boxes (32 / 64 /
 // 128 rows): the copy covers rows rounded up to 32.  dst is the tile's first row.
 __device__ __forceinline__ int act_rows_loaded(int rows) { return (rows + 31) & ~31; }
@@ -185,41 +180,96 @@ __device__ __forceinline__ int64_t total_items(const TileSource& src) {
 // ---- which items a CTA works on
 // With a device counter the CTAs draw items as they go (the first one is blockIdx.x, the
 // k-th draw yields gridDim.x + k), which evens out tiles of very different sizes; without
-// one, item k of a CTA is blockIdx.x + k * gridDim.x.  All roles of a CTA must see the same
-// sequence: one fetch thread publishes it through a small ring in shared memory (a full
-// and an empty mbarrier per slot), every other warp reads it in order.  -1 ends the sequence.
+// one, item k of a CTA is blockIdx.x + k * gridDim.x.  A fetch warp resolves each item -
+// tile record, problem width, first pool cell, rows of a gather tile: a chain of three
+// dependent global loads - one item ahead of the other roles and publishes the result in
+// a small ring in shared memory (a full and an empty mbarrier per slot).  Every other
+// warp reads the ring in order, so all roles see the same sequence and none of them waits
+// for global memory at an item boundary.
 constexpr int kItemRing = 2;
-struct ItemFeed {
-  uint32_t full0, empty0, ring0;                       // shared-memory addresses
+struct ItemSlot {
+  TileInfo ti;                                         // ti.valid: 1 work, 0 skip, -1 end of the sequence
+  int h;                                               // shrink: the problem's h_in; expand: its h_out
+  int pad_;
+  const void* ybase;                                   // expand: the problem's Y
+  int grow[kGatherRows];                               // rows of a gather tile
 };
-__device__ __forceinline__ int64_t next_item(const TileSource& src, const ItemFeed& f, uint32_t k,
-                                             int64_t total, volatile int* abort_flag) {
-  if (src.item_counter == nullptr) {
-    const int64_t it = (int64_t)blockIdx.x + (int64_t)k * gridDim.x;
-    return it < total ? it : -1;
-  }
-  long long item = -1;
-  if ((threadIdx.x & 31) == 0) {
-    const uint32_t s = k % kItemRing;
-    if (mbar_wait(f.full0 + 8u * s, (k / kItemRing) & 1, abort_flag)) {
-      asm volatile("ld.shared.s64 %0, [%1];" : "=l"(item) : "r"(f.ring0 + 8u * s));
-      mbar_arrive(f.empty0 + 8u * s);
-    }
-  }
-  return __shfl_sync(0xffffffffu, item, 0);
+struct ItemFeed {
+  uint32_t full0, empty0;                              // shared-memory addresses of the barriers
+  ItemSlot* slots;
+};
+// Consumer side; all 32 lanes call these.  tile_wait returns the slot of item k (null if a
+// bounded wait gave up); the caller copies what it needs and hands the slot back.
+__device__ __forceinline__ const ItemSlot* tile_wait(const ItemFeed& f, uint32_t k,
+                                                     volatile int* abort_flag) {
+  const uint32_t s = k % kItemRing;
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(f.full0 + 8u * s, (k / kItemRing) & 1, abort_flag);
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();
+  return ok ? f.slots + s : nullptr;
 }
-// The fetch thread's loop (one lane of a warp that has nothing else to do).
-__device__ __forceinline__ void feed_items(const TileSource& src, const ItemFeed& f, int64_t total,
+__device__ __forceinline__ void tile_release(const ItemFeed& f, uint32_t k) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(f.empty0 + 8u * (k % kItemRing));
+}
+__device__ __forceinline__ bool next_tile(const ItemFeed& f, uint32_t k, volatile int* abort_flag,
+                                          TileInfo& ti, int& h, const void*& ybase, int& grow_lane) {
+  const ItemSlot* sl = tile_wait(f, k, abort_flag);
+  if (sl == nullptr) return false;
+  ti = sl->ti;
+  h = sl->h;
+  ybase = sl->ybase;
+  grow_lane = sl->grow[threadIdx.x & (kGatherRows - 1)];
+  tile_release(f, k);
+  return ti.valid >= 0;
+}
+// The fetch warp's loop (all 32 lanes: get_tile is warp-collective).
+__device__ __forceinline__ void feed_tiles(const TileSource& src, const ItemFeed& f, int64_t total,
+                                           bool expand, int h_arg, const void* y_arg,
                                            volatile int* abort_flag) {
-  if (src.item_counter == nullptr) return;
+  const int lane = threadIdx.x & 31;
   for (uint32_t k = 0;; ++k) {
     const uint32_t s = k % kItemRing;
-    if (!mbar_wait(f.empty0 + 8u * s, ((k / kItemRing) & 1) ^ 1, abort_flag)) return;
-    long long item = k == 0 ? (long long)blockIdx.x
-                            : (long long)gridDim.x + (long long)atomicAdd(src.item_counter, 1u);
-    if (item >= total) item = -1;
-    asm volatile("st.shared.s64 [%0], %1;" ::"r"(f.ring0 + 8u * s), "l"(item) : "memory");
-    mbar_arrive(f.full0 + 8u * s);
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(f.empty0 + 8u * s, ((k / kItemRing) & 1) ^ 1, abort_flag);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return;
+    long long item = 0;
+    if (lane == 0) {
+      if (src.item_counter == nullptr) item = (long long)blockIdx.x + (long long)k * gridDim.x;
+      else item = k == 0 ? (long long)blockIdx.x
+                         : (long long)gridDim.x + (long long)atomicAdd(src.item_counter, 1u);
+      if (item >= total) item = -1;
+    }
+    item = __shfl_sync(0xffffffffu, item, 0);
+    TileInfo ti;
+    ti.valid = -1;
+    ti.gather = 0;
+    ti.rows = 0;
+    ti.row0 = 0;
+    ti.problem = 0;
+    if (item >= 0) ti = get_tile(src, item, expand);
+    int h = h_arg;
+    const void* yb = y_arg;
+    int g = 0;
+    if (ti.valid > 0) {
+      if (src.plan != nullptr) {
+        const StepProblem& sp = src.plan[ti.problem];
+        h = expand ? sp.h_out : sp.h_in;
+        yb = sp.y;
+      }
+      if (ti.gather && lane < ti.rows) g = src.gather_rows[ti.row0 + lane];
+    }
+    ItemSlot* sl = f.slots + s;
+    if (lane == 0) {
+      sl->ti = ti;
+      sl->h = h;
+      sl->ybase = yb;
+    }
+    if (lane < kGatherRows) sl->grow[lane] = g;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(f.full0 + 8u * s);
     if (item < 0) return;
   }
 }
@@ -245,11 +295,11 @@ __device__ __forceinline__ void trace_stamp(const TileSource& src, uint32_t k, i
 // is bytes in flight per SM against a memory latency of roughly 2 us under load.
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kShrinkMaxStages = 12;
-constexpr int kShrinkMaxSub = 4;                       // K blocks per stage, at most
+constexpr int kShrinkMaxSub = 16;                      // K blocks per stage, at most
 // The A operand of an MMA is a window of 128 rows (16 KB) from where a block's
 // activation rows start, whatever was loaded there: the window of the ring's last
 // block runs past the ring, so that much shared memory is allocated behind it.
-constexpr int kShrinkSmem = 1024 + kRingBytes + 512 + kTileM * 128;
+constexpr int kShrinkSmem = 1024 + kRingBytes + 512 + 512 + kTileM * 128;   // + barriers, item slots, window slack
 
 // A stage holds as many K blocks as fit: a block = the tile's activation rows
 // (2 KB for gathered rows, 4..16 KB for consecutive ones) then the adapter's rank
@@ -288,7 +338,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
   ItemFeed feed;
   feed.full0 = bars + 8u * (2 * kShrinkMaxStages + 4);
   feed.empty0 = feed.full0 + 8u * kItemRing;
-  feed.ring0 = bars + 384u;
+  feed.slots = reinterpret_cast<ItemSlot*>(smem_raw + (bars + 512u - smem_u32(smem_raw)));
   auto x_stage = [&](int s) { return base + (uint32_t)s * stage_bytes; };
 
   if (threadIdx.x == 0) {
@@ -321,9 +371,6 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
   // epilogue adds the partial sums.
   auto acc_stride = [](int n_pad) { return n_pad <= 64 ? 64 : 128; };
 
-  // per-item problem view
-  auto h_in_of = [&](const TileInfo& ti) { return src.plan ? src.plan[ti.problem].h_in : h_in_; };
-
   if (warp < kShrinkProducers) {
     // ------------------------------------------------------------ producers (stage k -> warp k % 3)
     // lane 0: TMA boxes (weights; consecutive activation rows).  Gather tiles: lane i
@@ -332,19 +379,19 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     uint32_t kiter = 0;
     bool ok = true;
     for (uint32_t ik = 0; ok; ++ik) {
-      const int64_t item = next_item(src, feed, ik, total, &abort_s);
-      if (item < 0) break;
-      const TileInfo ti = get_tile(src, item, false);
+      TileInfo ti;
+      int hw, grow_l;
+      const void* yb;
+      if (!next_tile(feed, ik, &abort_s, ti, hw, yb, grow_l)) break;
       if (!ti.valid) continue;
       const MapSet* ms = src.plan ? &src.plan[ti.problem].shrink : &maps_;
-      const T* xg = src.plan ? reinterpret_cast<const T*>(src.plan[ti.problem].x) : x_;
-      const int h_in = h_in_of(ti);
+      const int h_in = hw;
       const int n_pad = (ti.rank + 15) & ~15;
       const int kblocks = (h_in + kBoxCols - 1) / kBoxCols;
       const SubLayout sl = sub_layout(ti, n_pad, stage_bytes);
       const int nstages = (kblocks + sl.kbs - 1) / sl.kbs;
       const bool mine = ti.gather && lane < ti.rows;
-      const int grow = mine ? src.gather_rows[ti.row0 + lane] : 0;
+      const int grow = mine ? grow_l : 0;
       if (lane < 8) prefetch_tensormap(lane < 3 ? &ms->act[lane] : lane < 7 ? &ms->w[lane - 3] : &ms->row);
       const uint32_t blk_bytes =
           (uint32_t)((ti.gather ? ti.rows : act_rows_loaded(ti.rows)) + n_pad) * 128u;
@@ -392,13 +439,14 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     uint32_t kiter = 0, li = 0;
     bool ok = true;
     for (uint32_t ik = 0; ok; ++ik) {
-      const int64_t item = next_item(src, feed, ik, total, &abort_s);
-      if (item < 0) break;
-      const TileInfo ti = get_tile(src, item, false);
+      TileInfo ti;
+      int hw, grow_l;
+      const void* yb;
+      if (!next_tile(feed, ik, &abort_s, ti, hw, yb, grow_l)) break;
       if (!ti.valid) continue;
       if (lane == 0) {
         const int n_pad = (ti.rank + 15) & ~15;
-        const int kblocks = (h_in_of(ti) + kBoxCols - 1) / kBoxCols;
+        const int kblocks = (hw + kBoxCols - 1) / kBoxCols;
         const uint32_t idesc = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, n_pad, 0);
         const int ab = li & 1;
         const uint32_t tacc = tmem_base + ab * 256;
@@ -438,9 +486,10 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     const int row = q * 32 + lane;
     uint32_t li = 0;
     for (uint32_t ik = 0;; ++ik) {
-      const int64_t item = next_item(src, feed, ik, total, &abort_s);
-      if (item < 0) break;
-      const TileInfo ti = get_tile(src, item, false);
+      TileInfo ti;
+      int hw, grow_l;
+      const void* yb;
+      if (!next_tile(feed, ik, &abort_s, ti, hw, yb, grow_l)) break;
       if (!ti.valid) continue;
       const int ab = li & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar(ab), (li >> 1) & 1, &abort_s))) break;
@@ -456,7 +505,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       const int trow = ti.gather ? (q == 0 && lane < kGatherRows ? lane : kTileM) : row;
       const bool warp_live = ti.gather ? q == 0 : q * 32 < ti.rows;
       if (warp_live) {
-        T* vrow = v + (int64_t)(trow < ti.rows ? tile_row(src, ti, trow) : 0) * v_pitch;
+        T* vrow = v + (int64_t)(trow < ti.rows ? (ti.gather ? grow_l : ti.row0 + trow) : 0) * v_pitch;
         const int astr = acc_stride(n_pad), nacc = 256 / astr;
         for (int c = 0; c < n_pad; c += 16) {
           uint32_t r[16];
@@ -497,7 +546,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     tc_fence_before();
   } else {
     // ------------------------------------------------------------ work items
-    if (lane == 0) feed_items(src, feed, total, &abort_s);
+    feed_tiles(src, feed, total, false, h_in_, nullptr, &abort_s);
   }
   __syncthreads();
   if (warp == kShrinkMmaWarp) {
@@ -526,7 +575,7 @@ constexpr int kExpABytes = 2 * kTileM * 128;           // V tile, two 64-column 
 // rank 128, 32 + 8 KB for a 256-column gather tile.  Launches that cannot meet a rank
 // above 64 run four 48 KB stages, the others three 64 KB stages.
 constexpr int kExpAccBufs = 4;                         // accumulators of 128 TMEM columns
-constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512;
+constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512 + 512;      // + barriers, item slots
 
 // A work item's output tiles.  Consecutive-row tiles use 128 columns per stage
 // (B 64-column blocks 16 KB apart).  Gather tiles stream almost only weights, so
@@ -534,9 +583,9 @@ constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512;
 // bytes in flight per stage.
 struct ExpRange { int nt_begin, nt_count, h_out, ncbt, tile_n; uint32_t bstride, yoff; };
 
-__device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileInfo& ti, int h_out_) {
+__device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileInfo& ti, int h_out) {
   ExpRange r;
-  r.h_out = src.plan ? src.plan[ti.problem].h_out : h_out_;
+  r.h_out = h_out;
   r.ncbt = (ti.gather && ti.rank <= 64) ? 4 : 2;
   r.tile_n = r.ncbt * kBoxCols;
   r.bstride = (uint32_t)(((ti.rank + 15) & ~15) * 128);
@@ -556,6 +605,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_s;
   __shared__ uint32_t tmem_base_s;
+  __shared__ int grow_s[kExpEpiWarps][kGatherRows];    // rows of the gather tile an epilogue warp works on
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t total = total_items(src);
@@ -576,7 +626,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
   ItemFeed feed;
   feed.full0 = bars + 8u * (2 * kExpMaxStages + 2 * kExpAccBufs + 2);
   feed.empty0 = feed.full0 + 8u * kItemRing;
-  feed.ring0 = bars + 384u;
+  feed.slots = reinterpret_cast<ItemSlot*>(smem_raw + (bars + 512u - smem_u32(smem_raw)));
 
   if (threadIdx.x == 0) {
     abort_s = 0;
@@ -614,17 +664,18 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t ik = 0; ok; ++ik) {
-      const int64_t item = next_item(src, feed, ik, total, &abort_s);
-      if (item < 0) break;
-      const TileInfo ti = get_tile(src, item, true);
+      TileInfo ti;
+      int hw, grow_l;
+      const void* yb;
+      if (!next_tile(feed, ik, &abort_s, ti, hw, yb, grow_l)) break;
       if (!ti.valid) continue;
-      const ExpRange er = exp_range(src, ti, h_out_);
+      const ExpRange er = exp_range(src, ti, hw);
       const MapSet* ms = src.plan ? &src.plan[ti.problem].expand : &maps_;
-      const T* yg = src.plan ? reinterpret_cast<const T*>(src.plan[ti.problem].y) : y_;
+      const T* yg = reinterpret_cast<const T*>(yb);
       const int k_pad = (ti.rank + 15) & ~15;
       const int y_rows = ti.gather ? ti.rows : act_rows_loaded(ti.rows);
       const bool mine = ti.gather && lane < ti.rows;
-      const T* yrow = mine ? yg + (int64_t)src.gather_rows[ti.row0 + lane] * er.h_out : yg;
+      const T* yrow = mine ? yg + (int64_t)grow_l * er.h_out : yg;
       if (lane < 7) prefetch_tensormap(lane < 3 ? &ms->act[lane] : &ms->w[lane - 3]);
       for (int t = 0; t < er.nt_count; ++t, ++it) {
         if ((int)(it % kExpProducers) != pw) continue;            // the other producer's stage
@@ -670,11 +721,12 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     uint32_t it = 0, li = 0;
     bool ok = true;
     for (uint32_t ik = 0; ok; ++ik) {
-      const int64_t item = next_item(src, feed, ik, total, &abort_s);
-      if (item < 0) break;
-      const TileInfo ti = get_tile(src, item, true);
+      TileInfo ti;
+      int hw, grow_l;
+      const void* yb;
+      if (!next_tile(feed, ik, &abort_s, ti, hw, yb, grow_l)) break;
       if (!ti.valid) continue;
-      const ExpRange er = exp_range(src, ti, h_out_);
+      const ExpRange er = exp_range(src, ti, hw);
       if (er.nt_count <= 0) continue;
       const int k_pad = (ti.rank + 15) & ~15;
       const int ksteps = k_pad / 16;
@@ -741,17 +793,28 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     uint32_t it = 0, li = 0;
     bool ok = true;
     for (uint32_t ik = 0; ok; ++ik) {
-      const int64_t item = next_item(src, feed, ik, total, &abort_s);
-      if (item < 0) break;
-      const TileInfo ti = get_tile(src, item, true);
+      TileInfo ti;
+      int hw, grow_l;
+      const void* yb;
+      {
+        const ItemSlot* sl = tile_wait(feed, ik, &abort_s);
+        if (sl == nullptr) break;
+        ti = sl->ti;
+        hw = sl->h;
+        yb = sl->ybase;
+        grow_l = sl->grow[lane & (kGatherRows - 1)];
+        if (lane < kGatherRows) grow_s[warp][lane] = grow_l;    // this warp's copy: the slot is recycled
+        tile_release(feed, ik);
+      }
+      const int* grow = grow_s[warp];
+      if (ti.valid < 0) break;
       if (!ti.valid) continue;
-      const ExpRange er = exp_range(src, ti, h_out_);
+      const ExpRange er = exp_range(src, ti, hw);
       if (er.nt_count <= 0) continue;
-      T* y = y_;
+      T* y = reinterpret_cast<T*>(const_cast<void*>(yb));
       const T* v = v_;
       int v_pitch = v_pitch_;
       if (src.plan != nullptr) {
-        y = reinterpret_cast<T*>(src.plan[ti.problem].y);
         v = reinterpret_cast<const T*>(src.vbuf) + (int64_t)ti.problem * src.vstride;
         v_pitch = kMaxRank;
       }
@@ -760,19 +823,13 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       // consecutive rows: lane = row.  Gather tiles: lane = output column (see the
       // epilogue), warp j takes the j-th 128-column half of a stage.
       const bool warp_live = ti.gather ? j < (er.ncbt >> 1) : q * 32 < ti.rows;
-      int grow[kGatherRows];
-      if (ti.gather) {
-#pragma unroll
-        for (int i = 0; i < kGatherRows; ++i)
-          grow[i] = i < ti.rows ? src.gather_rows[ti.row0 + i] : 0;
-      }
       // ---- stage V as the K-major, 128-byte-swizzled A operand (zeros beyond rank / rows)
       ok = __all_sync(0xffffffffu, mbar_wait(a_free_bar, (li & 1) ^ 1, &abort_s));
       if (!ok) break;
       {
         const int vr = et & 127;                       // row slot
         const int vt = vr;                             // gathered rows sit densely in slots 0..15
-        const T* vrow = v + (int64_t)(vt < ti.rows ? tile_row(src, ti, vt) : 0) * v_pitch;
+        const T* vrow = v + (int64_t)(vt < ti.rows ? (ti.gather ? grow_l : ti.row0 + vt) : 0) * v_pitch;
         for (int c8 = et >> 7; c8 < k_pad / 8; c8 += kExpEpiWarps / 4) {
           uint4 val = make_uint4(0, 0, 0, 0);
           if (vt < ti.rows && c8 * 8 < ti.rank) val = ldg128(vrow + c8 * 8);
@@ -892,7 +949,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     tc_fence_before();
   } else if (warp == kExpFetchWarp) {
     // ------------------------------------------------------------ work items
-    if (lane == 0) feed_items(src, feed, total, &abort_s);
+    feed_tiles(src, feed, total, true, h_out_, y_, &abort_s);
   }
   __syncthreads();
   if (warp == kExpMmaWarp) {

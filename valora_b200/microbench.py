@@ -1,8 +1,10 @@
-"""Micro-benchmarks of the drop-in operator calls on one B200.
+"""Micro-benchmarks on one B200, one JSON line each.
 
-    python -m valora_b200.microbench --config 1     # decode BGMV, bf16, 512 tokens
+    python -m valora_b200.microbench --config 1     # decode BGMV drop-in call, bf16, 512 tokens
+    python -m valora_b200.microbench --config 2     # prefill, mixed ranks 8..128, fp16, 7 projections (step API)
+    python -m valora_b200.microbench --config 4     # 16384 tokens, 1024 adapters, ranks 16..128, bf16 (step API)
 
-Prints one JSON line.  A measurement walks `--layers` independent copies
+Config 1:  A measurement walks `--layers` independent copies
 of the operator's tensors (own pools, own activations; together larger than
 L2), one shrink and one expand call per copy, and times the walk with CUDA
 events on the launching stream; GB/s are algorithmic bytes (activations once,
@@ -139,10 +141,57 @@ def bench_bgmv(layers: int, reps: int, warmup: int, dev, eager: bool = False):
     }
 
 
+def bench_step(config: int, layers: int, reps: int, warmup: int, dev):
+    """Configs 2 and 4 through LoraStepEngine.step (device packer + one shrink and one
+    expand launch): `layers` copies of the config's projections, every copy with its
+    own pools and activations, CUDA events around each stage."""
+    from .engine import LoraStepEngine
+    b = workloads.CONFIGS[config]()
+    b.layers = layers
+    eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T)
+    eng.randomize_weights(seed=b.seed)
+    g = torch.Generator(device=dev)
+    g.manual_seed(b.seed)
+    for l in range(layers):
+        for p in range(len(b.projections)):
+            eng.x[l][p].normal_(generator=g)
+            eng.y[l][p].normal_(generator=g)
+    tok = torch.from_numpy(b.tok_adapter.astype(np.int64)).to(dev)
+    for _ in range(warmup):
+        packed = eng.step(tok)
+    torch.cuda.synchronize()
+    counts = packed.host_counts()
+    names = ["pack"] + [n for n, _ in eng.phases()]
+    ms = {n: [] for n in names}
+    tot = []
+    for _ in range(reps):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+        eng.step_timed(tok, ev)
+        torch.cuda.synchronize()
+        for i, n in enumerate(names):
+            ms[n].append(ev[i].elapsed_time(ev[i + 1]))
+        tot.append(ev[0].elapsed_time(ev[-1]))
+    if ops.device_status() != 0:
+        raise SystemExit("a bounded wait gave up inside a kernel")
+    peak, src = _peak()
+    step_ms = float(np.median(tot))
+    nbytes, flops = b.algorithmic_bytes(), b.algorithmic_flops()
+    return {
+        "bench": "lora_step", "workload": b.name, "dtype": str(b.dtype).replace("torch.", ""), "tokens": b.T,
+        "adapters": b.n_adapters, "adapters_touched": int(len(b.touched())),
+        "ranks": sorted(set(int(r) for r in b.ranks)), "projections": len(b.projections), "layers": layers,
+        "mma_tiles": counts["n_mma"], "gather_tiles": counts["n_gather"],
+        "ms_per_step": step_ms, "phase_ms": {n: float(np.median(v)) for n, v in ms.items()},
+        "tokens_per_s": b.T / (step_ms * 1e-3), "algorithmic_bytes": nbytes,
+        "gbs": nbytes / (step_ms * 1e-3) / 1e9, "frac": nbytes / (step_ms * 1e-3) / 1e9 / peak,
+        "tflops": flops / (step_ms * 1e-3) / 1e12, "peak_gbs": peak, "peak_source": src,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, default=1, choices=[1])
-    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 4])
+    ap.add_argument("--layers", type=int, default=0, help="independent copies walked (default: 32 / 4 / 8)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--eager", action="store_true", help="launch call by call (no CUDA graph), for profilers")
@@ -151,7 +200,11 @@ def main():
         raise SystemExit("microbench needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    print(json.dumps(bench_bgmv(args.layers, args.reps, args.warmup, dev, args.eager)))
+    if args.config == 1:
+        print(json.dumps(bench_bgmv(args.layers or 32, args.reps, args.warmup, dev, args.eager)))
+    else:
+        print(json.dumps(bench_step(args.config, args.layers or (4 if args.config == 2 else 8), args.reps,
+                                    args.warmup, dev)))
 
 
 if __name__ == "__main__":
