@@ -246,6 +246,12 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
  * two SIMT gather launches are skipped.  gather_rows_per_tile must be <= 16 with
  * this flag and <= 8 without it.  Plans need h_in and h_out multiples of 64. */
 #define VLR_STEP_GATHER_ON_TENSOR_CORES 16
+/* or-ed into phase_mask together with VLR_STEP_GATHER_ON_TENSOR_CORES: a gather
+ * stage of the expand carries as many 64-column blocks as the stage holds (up to
+ * 1024 columns) instead of at most four.  Pays when the batch has adapters of
+ * rank 32 or less (their weight rows fill a fraction of a stage otherwise); at
+ * rank 64 the plain form is the faster one. */
+#define VLR_STEP_WIDE_GATHER_STAGES 32
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
                   const int32_t* counts, const void* scales, int max_h_in, int max_h_out,

@@ -583,12 +583,20 @@ constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512 + 512;      // + b
 // bytes in flight per stage.
 struct ExpRange { int nt_begin, nt_count, h_out, ncbt, tile_n; uint32_t bstride, yoff; };
 
+// WIDE: a gather stage takes as many 64-column blocks (weights + 16 Y row pieces each) as
+// it holds - an even number, at most 16 (8 chains of 128 columns x 16 accumulator columns
+// each) - and keeps its Y rows row-major, one copy per row.  For batches with small ranks.
+template <bool WIDE>
 __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileInfo& ti, int h_out) {
   ExpRange r;
   r.h_out = h_out;
-  r.ncbt = (ti.gather && ti.rank <= 64) ? 4 : 2;
-  r.tile_n = r.ncbt * kBoxCols;
   r.bstride = (uint32_t)(((ti.rank + 15) & ~15) * 128);
+  r.ncbt = (ti.gather && ti.rank <= 64) ? 4 : 2;
+  if (WIDE && ti.gather) {
+    const int n = (int)((uint32_t)src.exp_stage_bytes / (r.bstride + kGatherRows * 128)) & ~1;
+    r.ncbt = n < 2 ? 2 : (n > 16 ? 16 : n);
+  }
+  r.tile_n = r.ncbt * kBoxCols;
   r.yoff = (uint32_t)r.ncbt * r.bstride;
   const int ntiles = (r.h_out + r.tile_n - 1) / r.tile_n;
   const int per = (ntiles + src.nsplit - 1) / src.nsplit;
@@ -597,7 +605,7 @@ __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileI
   return r;
 }
 
-template <typename T, int NST>
+template <typename T, int NST, bool WIDE>
 __global__ void __launch_bounds__(kExpThreads, 1)
 atmm_expand_kernel(const __grid_constant__ MapSet maps_,
                    T* __restrict__ y_, const T* __restrict__ v_, const T* __restrict__ scales,
@@ -669,7 +677,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       const void* yb;
       if (!next_tile(feed, ik, &abort_s, ti, hw, yb, grow_l)) break;
       if (!ti.valid) continue;
-      const ExpRange er = exp_range(src, ti, hw);
+      const ExpRange er = exp_range<WIDE>(src, ti, hw);
       const MapSet* ms = src.plan ? &src.plan[ti.problem].expand : &maps_;
       const T* yg = reinterpret_cast<const T*>(yb);
       const int k_pad = (ti.rank + 15) & ~15;
@@ -686,7 +694,10 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
           ok = mbar_wait(empty_bar(s), ((it / nst) & 1) ^ 1, &abort_s);
           if (ok) {
             trace_stamp(src, it, 0);
-            const uint32_t bytes = (uint32_t)ncb * (uint32_t)(k_pad + y_rows) * 128u;
+            uint32_t bytes = (uint32_t)ncb * (uint32_t)(k_pad + y_rows) * 128u;
+            if (WIDE && ti.gather)
+              bytes = (uint32_t)ncb * (uint32_t)k_pad * 128u +
+                      (uint32_t)y_rows * (uint32_t)min(er.tile_n, er.h_out - n0) * 2u;
             mbar_expect_tx(full_bar(s), bytes);
             for (int cb = 0; cb < ncb; ++cb)
               load_w_rows(b_stage(s) + cb * er.bstride, ms, n0 + cb * kBoxCols, (int)ti.wrow0,
@@ -701,10 +712,15 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         if (ti.gather) {
           ok = __shfl_sync(0xffffffffu, ok, 0);        // also orders expect_tx before the copies
           if (!ok) break;
-          if (mine)
+          if (WIDE) {
+            if (mine)
+              bulk_load_1d((b_stage(s) + er.yoff) + lane * (er.tile_n * 2), yrow + n0,
+                           (uint32_t)min(er.tile_n, er.h_out - n0) * 2u, full_bar(s));
+          } else if (mine) {
             for (int cb = 0; cb < ncb; ++cb)
               bulk_load_1d((b_stage(s) + er.yoff) + cb * (kGatherRows * 128) + lane * 128,
                            yrow + n0 + cb * kBoxCols, 128, full_bar(s));
+          }
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -726,7 +742,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       const void* yb;
       if (!next_tile(feed, ik, &abort_s, ti, hw, yb, grow_l)) break;
       if (!ti.valid) continue;
-      const ExpRange er = exp_range(src, ti, hw);
+      const ExpRange er = exp_range<WIDE>(src, ti, hw);
       if (er.nt_count <= 0) continue;
       const int k_pad = (ti.rank + 15) & ~15;
       const int ksteps = k_pad / 16;
@@ -758,12 +774,14 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
             // D^T[128 cols x 16 rows] = B^T[128 x k] * V^T[k x 16], one chain per 128 columns:
             // A operand = the staged B tile read MN-major (two 64-column blocks bstride
             // apart), B operand = the V rows, K-major, N = 16.
+            // accumulator chains 32 columns apart, or 16 where a stage may hold eight of them
+            constexpr int kChainCols = WIDE ? 16 : 32;
             for (int mt = 0; mt < (er.ncbt >> 1); ++mt)
               for (int j = 0; j < ksteps; ++j) {
                 const uint64_t ad = smem_desc_sw128(b_stage(s) + mt * 2 * er.bstride + j * (kBoxRowsW * 128),
                                                     er.bstride, 1024);
                 const uint64_t bd = smem_desc_sw128(a_tile + (j >> 2) * (kTileM * 128) + (j & 3) * 32, 16, 1024);
-                umma_f16(tmem_base + ab * 128 + mt * 32, ad, bd, idesc_g, j != 0);
+                umma_f16(tmem_base + ab * 128 + mt * kChainCols, ad, bd, idesc_g, j != 0);
               }
           } else {
             for (int j = 0; j < ksteps; ++j) {
@@ -809,7 +827,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       const int* grow = grow_s[warp];
       if (ti.valid < 0) break;
       if (!ti.valid) continue;
-      const ExpRange er = exp_range(src, ti, hw);
+      const ExpRange er = exp_range<WIDE>(src, ti, hw);
       if (er.nt_count <= 0) continue;
       T* y = reinterpret_cast<T*>(const_cast<void*>(yb));
       const T* v = v_;
@@ -852,27 +870,66 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         if (ti.gather) {
           // gathered rows, transposed product: this lane owns output column colt of the
           // stage's tile and gets the 16 row values of that column from tensor memory
-          const int colt = j * 128 + q * 32 + lane;
-          const int col = n0 + colt;
-          uint32_t r[kGatherRows];
-          uint32_t yv[kGatherRows];
-          if (warp_live) {
-            tmem_ld_32x16(tacc + j * 32, r);
-            const uint32_t yaddr = (b_stage(s) + er.yoff) + (colt >> 6) * (kGatherRows * 128) + (colt & 63) * 2;
+          if constexpr (WIDE) {
+            // warp (q, j) takes the chains j, j + 2, ... of 128 columns; within a chain this lane
+            // owns column q * 32 + lane.  Row-major Y tile, tile_n columns wide.  The accumulator
+            // is handed back once this warp's last chain is in registers.
+            const int nchains = er.ncbt >> 1;
+            const uint32_t ytile = b_stage(s) + er.yoff;
+            const uint32_t ypitch = (uint32_t)er.tile_n * 2u;
+            for (int mt = j; mt < nchains; mt += 2) {
+              const int colt = mt * 128 + q * 32 + lane;
+              const int col = n0 + colt;
+              uint32_t r[kGatherRows];
+              uint32_t yv[kGatherRows];
+              tmem_ld_32x16(tacc + mt * 16, r);
 #pragma unroll
-            for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(yaddr + i * 128);
-            tmem_ld_wait();
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(ab));
-          if (warp_live && col < h_out) {
+              for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(ytile + i * ypitch + colt * 2);
+              tmem_ld_wait();
+              if (mt + 2 >= nchains) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(ab));
+              }
+              if (col < h_out) {
 #pragma unroll
-            for (int i = 0; i < kGatherRows; ++i) {
-              if (i < ti.rows) {
-                const uint16_t y16 = (uint16_t)yv[i];
-                const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
-                y[(int64_t)grow[i] * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
+                for (int i = 0; i < kGatherRows; ++i) {
+                  if (i < ti.rows) {
+                    const uint16_t y16 = (uint16_t)yv[i];
+                    const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
+                    y[(int64_t)grow[i] * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
+                  }
+                }
+              }
+            }
+            if (j >= nchains) {                        // a warp without a chain in this stage
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(ab));
+            }
+          } else {
+            const int colt = j * 128 + q * 32 + lane;
+            const int col = n0 + colt;
+            uint32_t r[kGatherRows];
+            uint32_t yv[kGatherRows];
+            if (warp_live) {
+              tmem_ld_32x16(tacc + j * 32, r);
+              const uint32_t yaddr = (b_stage(s) + er.yoff) + (colt >> 6) * (kGatherRows * 128) + (colt & 63) * 2;
+  #pragma unroll
+              for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(yaddr + i * 128);
+              tmem_ld_wait();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(ab));
+            if (warp_live && col < h_out) {
+  #pragma unroll
+              for (int i = 0; i < kGatherRows; ++i) {
+                if (i < ti.rows) {
+                  const uint16_t y16 = (uint16_t)yv[i];
+                  const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
+                  y[(int64_t)grow[i] * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
+                }
               }
             }
           }
@@ -1043,10 +1100,14 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
     set((const void*)atmm_shrink_kernel<__half, 4>, kShrinkSmem);
     set((const void*)atmm_shrink_kernel<__nv_bfloat16, 3>, kShrinkSmem);
     set((const void*)atmm_shrink_kernel<__nv_bfloat16, 4>, kShrinkSmem);
-    set((const void*)atmm_expand_kernel<__half, 3>, kExpSmem);
-    set((const void*)atmm_expand_kernel<__half, 4>, kExpSmem);
-    set((const void*)atmm_expand_kernel<__nv_bfloat16, 3>, kExpSmem);
-    set((const void*)atmm_expand_kernel<__nv_bfloat16, 4>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__half, 3, false>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__half, 4, false>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 3, false>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 4, false>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__half, 3, true>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__half, 4, true>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 3, true>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 4, true>, kExpSmem);
     if (e != cudaSuccess) {
       cudaGetLastError();
       return (int)e;
@@ -1088,11 +1149,17 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
     const int64_t items = max_tiles * n_problems * src.nsplit;
     const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
     const int sc = (flags & VLR_ATMM_APPLY_SCALE) ? 1 : 0;
-    if (src.exp_stages == 4)
-      atmm_expand_kernel<T, 4><<<grid, kExpThreads, kExpSmem, stream>>>(
+    if (src.exp_stages == 4 && !src.wide_gather)
+      atmm_expand_kernel<T, 4, false><<<grid, kExpThreads, kExpSmem, stream>>>(
+          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
+    else if (src.exp_stages == 4)
+      atmm_expand_kernel<T, 4, true><<<grid, kExpThreads, kExpSmem, stream>>>(
+          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
+    else if (!src.wide_gather)
+      atmm_expand_kernel<T, 3, false><<<grid, kExpThreads, kExpSmem, stream>>>(
           maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
     else
-      atmm_expand_kernel<T, 3><<<grid, kExpThreads, kExpSmem, stream>>>(
+      atmm_expand_kernel<T, 3, true><<<grid, kExpThreads, kExpSmem, stream>>>(
           maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
   }
   return launch_status();

@@ -72,6 +72,7 @@ struct TileSource {
   const int32_t* counts;
   const int32_t* gather_rows;
   int gather_mma;                    // 1: gather tiles are work items of the tensor-core kernels too
+  int wide_gather;                   // 1: expand gather stages take as many column blocks as fit (small ranks)
   // adapter tables
   const int64_t* a_start;
   const int64_t* a_loc;

@@ -132,7 +132,11 @@ class LoraStepEngine:
         return packed
 
     def _gather_flag(self) -> int:
-        return ops.STEP_GATHER_ON_TENSOR_CORES if self.gather_path == "mma" else 0
+        if self.gather_path != "mma":
+            return 0
+        # adapters of rank 32 or less: let a gather stage of the expand take more columns
+        wide = ops.STEP_WIDE_GATHER_STAGES if min(self.ranks) <= 32 else 0
+        return ops.STEP_GATHER_ON_TENSOR_CORES | wide
 
     def phases(self):
         """(name, phase bit) of the kernel launches of one step, in order."""

@@ -19,6 +19,7 @@ TILE_INTS, COUNT_INTS = 8, 8
 MAX_RANK = 128
 PHASE_SHRINK_MMA, PHASE_SHRINK_GATHER, PHASE_EXPAND_MMA, PHASE_EXPAND_GATHER, PHASE_ALL = 1, 2, 4, 8, 15
 STEP_GATHER_ON_TENSOR_CORES = 16
+STEP_WIDE_GATHER_STAGES = 32
 
 
 def _dtype_code(t: torch.Tensor) -> int:
