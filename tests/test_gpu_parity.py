@@ -362,11 +362,11 @@ def test_dropin_modules(ops):
 
 
 # --------------------------------------------------------------------------- step (packed batch, many problems)
-def _step_case(ops, batch, proj_ids, layers=1, mma_min=16, gather_path="mma"):
+def _step_case(ops, batch, proj_ids, layers=1, mma_min=16, gather_path="mma", wide_gather=None):
     from valora_b200.engine import LoraStepEngine
     projs = [batch.projections[p] for p in proj_ids]
     eng = LoraStepEngine(projs, batch.ranks, batch.scalings(), batch.dtype, DEV, layers, batch.T,
-                         mma_min_rows=mma_min, gather_path=gather_path)
+                         mma_min_rows=mma_min, gather_path=gather_path, wide_gather=wide_gather)
     g = torch.Generator().manual_seed(batch.seed)
     W = {}
     for layer in range(layers):
@@ -470,6 +470,15 @@ def test_step_narrow_projections(ops, gather_path):
     b = workloads.config0()
     b.projections = [("a", 64, 64), ("b", 64, 192), ("c", 128, 64)]
     _step_case(ops, b, [0, 1, 2], layers=2, gather_path=gather_path)
+
+
+@pytest.mark.parametrize("wide", [False, True])
+def test_step_gather_stage_forms(ops, wide):
+    """both forms of the expand's gather stages (at most four 64-column blocks / as many as fit)
+    on both kinds of batch: rank 64 everywhere (config 3, 4096 -> 11008) and ranks 16..128 with
+    mostly decode rows (config 4 slice)"""
+    _step_case(ops, workloads.config3(layers=1), [4], wide_gather=wide)
+    _step_case(ops, workloads.config4(n_gpus=8, rank=5), [0], wide_gather=wide)
 
 
 def test_step_gathered_rows_mixed_ranks(ops):

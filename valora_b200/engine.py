@@ -27,14 +27,17 @@ class LoraStepEngine:
     def __init__(self, projections: Sequence[Tuple[str, int, int]], ranks: Sequence[int],
                  scalings: Sequence[float], dtype, device, layers: int, max_tokens: int,
                  tile_m: int = 128, mma_min_rows: int = 16, gather_rows_per_tile: Optional[int] = None,
-                 alloc_activations: bool = True, gather_path: str = "mma"):
+                 alloc_activations: bool = True, gather_path: str = "mma",
+                 wide_gather: Optional[bool] = None):
         """gather_path: "mma" sends rows that are not consecutive in the batch (decode
         tokens) through the tensor-core kernels with gathered rows (up to 128 rows of
         an adapter per tile); "simt" sends them through the gather mat-vec kernels
-        (8 rows per tile)."""
+        (8 rows per tile).  wide_gather: let a gather stage of the expand take as many
+        columns as fit (default: when an adapter of rank 32 or less is resident)."""
         if gather_path not in ("mma", "simt"):
             raise ValueError("gather_path must be 'mma' or 'simt'")
         self.gather_path = gather_path
+        self.wide_gather = wide_gather
         if gather_rows_per_tile is None:
             gather_rows_per_tile = 16 if gather_path == "mma" else 8
         if gather_path == "simt" and gather_rows_per_tile > 8:
@@ -135,7 +138,8 @@ class LoraStepEngine:
         if self.gather_path != "mma":
             return 0
         # adapters of rank 32 or less: let a gather stage of the expand take more columns
-        wide = ops.STEP_WIDE_GATHER_STAGES if min(self.ranks) <= 32 else 0
+        on = min(self.ranks) <= 32 if self.wide_gather is None else bool(self.wide_gather)
+        wide = ops.STEP_WIDE_GATHER_STAGES if on else 0
         return ops.STEP_GATHER_ON_TENSOR_CORES | wide
 
     def phases(self):
