@@ -1,6 +1,7 @@
 """Micro-benchmarks on one B200, one JSON line each.
 
     python -m valora_b200.microbench --config 1     # decode BGMV drop-in call, bf16, 512 tokens
+    python -m valora_b200.microbench --config 1 --api step   # the same decode batch through the step API
     python -m valora_b200.microbench --config 2     # prefill, mixed ranks 8..128, fp16, 7 projections (step API)
     python -m valora_b200.microbench --config 4     # 16384 tokens, 1024 adapters, ranks 16..128, bf16 (step API)
 
@@ -195,16 +196,18 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--eager", action="store_true", help="launch call by call (no CUDA graph), for profilers")
+    ap.add_argument("--api", default="auto", choices=["auto", "dropin", "step"],
+                    help="config 1 only: the 9-argument decode call (default) or the step API")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    if args.config == 1:
+    if args.config == 1 and args.api != "step":
         print(json.dumps(bench_bgmv(args.layers or 32, args.reps, args.warmup, dev, args.eager)))
     else:
-        print(json.dumps(bench_step(args.config, args.layers or (4 if args.config == 2 else 8), args.reps,
-                                    args.warmup, dev)))
+        default_layers = {1: 32, 2: 4, 4: 8}[args.config]
+        print(json.dumps(bench_step(args.config, args.layers or default_layers, args.reps, args.warmup, dev)))
 
 
 if __name__ == "__main__":
