@@ -361,6 +361,64 @@ def test_dropin_modules(ops):
     assert _err(v2, ref) <= TOL
 
 
+def test_dropin_replays_a_layer_of_the_callers_sequence(ops):
+    """The operator calls of one layer in the order the reference's caller issues them
+    (lora_unordered_batch_infer.py:946-988 for q/k/v, :1611-1622 for o): three shrinks
+    into zeroed [T, max_r] buffers (slots 0..2), three expands into q / k / v, then
+    shrink + expand of slot 3 on the attention output - through the installed module
+    names, with the problem table coming from the device packer instead of
+    set_sgmm_args.  Reference semantics: no adapter scale in the ATMM expand."""
+    from valora_b200 import dropin
+    dropin.install(force=True)
+    from atmm_ops import dispatch_bgmv as dispatch_sgmm
+    dtype, H = torch.float16, 512
+    ranks = [16, 64, 32]
+    req_ad = [1, 0, 2, 1, 1, 0]
+    req_len = [70, 130, 1, 1, 45, 9]
+    tok = np.repeat(req_ad, req_len).astype(np.int64)
+    T, max_r = tok.shape[0], max(ranks)
+    A, B = rand_lora(ranks, H, H, dtype, n_slots=4, seed=21, wstd=0.05)
+    a_start, a_len, a_loc, total = build_tables(ranks, 4, shuffle=True, contiguous_slots=True, seed=3)
+    key_buffer = fill_pool_a(A, ranks, a_start, a_loc, total, H, dtype).view(total, 8, H // 8).to(DEV)
+    value_buffer = fill_pool_b(B, ranks, a_start, a_loc, total, H, dtype, layout="rows").view(total, 8, H // 8).to(DEV)
+    ast_d, alen_d, aloc_d = t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV)
+    scaling = torch.ones(len(ranks), dtype=dtype, device=DEV)
+    # the batch's problem table, in request order (the reference's run-length encoding)
+    packer = ops.Packer(T, len(ranks), DEV)
+    pk = packer.pack(torch.from_numpy(tok).to(DEV), alen_d, sort=False)
+    P = pk.host_counts()["P"]
+    tables = (pk.seg_len, pk.seg_rank, pk.seg_adapter, pk.seg_start)
+    tmp_d = torch.zeros(60 * 128, dtype=torch.int8, device=DEV)
+    tiles = (64, 32, 32, 32, 32, 32)
+    bins = torch.from_numpy(tok).to(DEV)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, H, generator=g).to(dtype)
+    outs0 = [torch.randn(T, H, generator=g).to(dtype) for _ in range(4)]        # q, k, v, o before LoRA
+    attn = torch.randn(T, H, generator=g).to(dtype)                             # input of the o projection
+    delta = [torch.zeros(T, max_r, dtype=dtype, device=DEV) for _ in range(4)]
+    outs = [o.to(DEV) for o in outs0]
+    xd, attnd = x.to(DEV), attn.to(DEV)
+    for slot in range(3):
+        dispatch_sgmm(delta[slot], xd, key_buffer, ast_d, alen_d, aloc_d, bins, slot, scaling, *tables, tmp_d, P, *tiles)
+    torch.cuda.synchronize()
+    for slot in range(3):
+        dispatch_sgmm(outs[slot], delta[slot], value_buffer, ast_d, alen_d, aloc_d, bins, slot, scaling, *tables,
+                      tmp_d, P, *tiles)
+    torch.cuda.synchronize()
+    dispatch_sgmm(delta[3], attnd, key_buffer, ast_d, alen_d, aloc_d, bins, 3, scaling, *tables, tmp_d, P, *tiles)
+    dispatch_sgmm(outs[3], delta[3], value_buffer, ast_d, alen_d, aloc_d, bins, 3, scaling, *tables, tmp_d, P, *tiles)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    oc, rc, li, si = (v[:P + (1 if i == 3 else 0)].cpu().numpy() for i, v in enumerate(tables))
+    wa, wb = key_buffer.cpu().view(total, H), value_buffer.cpu().view(total, H)
+    for slot in range(4):
+        src = attn if slot == 3 else x
+        v_ref = oracle.atmm_shrink_ref(torch.zeros(T, max_r, dtype=dtype), src, wa, a_start, a_loc, slot, oc, rc, li, si, P)
+        assert _err(delta[slot], v_ref) <= TOL
+        y_ref = oracle.atmm_expand_ref(outs0[slot], v_ref.to(dtype), wb, a_start, a_loc, slot, oc, rc, li, si, P)
+        assert _err(outs[slot], y_ref) <= TOL
+
+
 # --------------------------------------------------------------------------- step (packed batch, many problems)
 def _step_case(ops, batch, proj_ids, layers=1, mma_min=16, gather_path="mma", wide_gather=None):
     from valora_b200.engine import LoraStepEngine
