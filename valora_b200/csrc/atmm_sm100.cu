@@ -2,10 +2,12 @@
 // tensor cores: tcgen05.mma with accumulators in tensor memory, operands staged
 // in shared memory by tiled bulk tensor copies (TMA) behind an mbarrier ring.
 //
-// One CTA = one tile of up to 128 consecutive rows of one segment.
-//   warp 0      TMA producer (one lane)
-//   warp 1      tensor-memory allocation, MMA issue (one lane)
-//   warps 2..5  epilogue, one TMEM lane quarter each
+// Persistent CTAs, one per SM, working through (problem, tile) items: a tile is up to 128
+// consecutive rows of one segment, or up to 16 gathered rows of one adapter.  Roles
+//   shrink: warps 0-2 TMA producers, 3 MMA issue + tensor-memory allocation,
+//           4-7 epilogue (one TMEM lane quarter each), 8 work-item fetch
+//   expand: warps 0-7 epilogue (lane quarter x 64-column block), 8-9 TMA producers,
+//           10 MMA issue, 11 work-item fetch
 // No cluster launch, no multicast copies, no peer memory.
 //
 // Shrink: A operand = X tile [128 x 64] (K-major), B operand = the adapter's A
@@ -283,8 +285,8 @@ __device__ __forceinline__ void trace_stamp(const TileSource& src, uint32_t k, i
 }
 
 // ============================================================================
-// shrink: persistent CTAs, 6-stage TMA ring over K, two accumulators in tensor
-// memory so the epilogue of one tile overlaps the main loop of the next.
+// shrink: persistent CTAs, TMA ring over K, two tile buffers in tensor memory so
+// the epilogue of one tile overlaps the main loop of the next.
 // ============================================================================
 // The operand ring is 192 KB.  A K block of a full tile is the X tile (16 KB) plus
 // the adapter's rank rows (8 KB at rank 64, 16 KB at rank 128); a stage holds two of
@@ -558,14 +560,15 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
 
 // ============================================================================
 // expand: persistent CTAs; per tile the V rows are staged once as the A operand,
-// then a 3-stage ring streams (B tile, Y tile) pairs, 128 output columns each.
+// then the ring streams (B tile, Y tile) pairs, 128 output columns each (more for
+// gather tiles).
 // ============================================================================
 constexpr int kExpMaxStages = 4;
 constexpr int kExpEpiWarps = 8;                        // 2 per TMEM lane quarter, 64 columns each
 constexpr int kExpEpiWarp0 = 0;                        // epilogue = warps 0..7
 constexpr int kExpProducers = 2;                       // producers = warps 8..9
 constexpr int kExpProdWarp0 = kExpEpiWarps;
-constexpr int kExpMmaWarp = kExpProdWarp0 + kExpProducers;   // warp 18
+constexpr int kExpMmaWarp = kExpProdWarp0 + kExpProducers;   // warp 10
 constexpr int kExpFetchWarp = kExpMmaWarp + 1;           // warp 11: draws work items
 constexpr int kExpThreads = 32 * (kExpFetchWarp + 1);
 constexpr int kExpTileN = 128;
