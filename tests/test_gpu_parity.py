@@ -419,6 +419,74 @@ def test_dropin_replays_a_layer_of_the_callers_sequence(ops):
         assert _err(outs[slot], y_ref) <= TOL
 
 
+def test_dropin_replays_the_merged_adapter_correction(ops):
+    """One adapter is folded into the base weight (merged mode) while requests of other
+    adapters share the batch.  The caller's correction (lora_unordered_batch_infer.py:
+    991-1063): the rows after the merged adapter's are stacked twice, the first copy runs
+    with each row's own adapter, the second with the merged adapter, and
+    `q[tk:] += out[:L] - out[L:]` takes the merged contribution out again.  Replayed
+    through the installed module name; the end result must be base + own adapter."""
+    from valora_b200 import dropin
+    dropin.install(force=True)
+    from atmm_ops import dispatch_bgmv as dispatch_sgmm
+    dtype, H = torch.float16, 512
+    ranks = [32, 16, 64, 16]
+    merged = 2
+    req_ad = [2, 2, 0, 1, 3, 0, 1, 1]                       # the merged adapter's requests lead the batch
+    req_len = [40, 1, 90, 1, 1, 33, 1, 150]
+    tok = np.repeat(req_ad, req_len).astype(np.int64)
+    T, max_r = tok.shape[0], max(ranks)
+    tk = int(sum(l for a, l in zip(req_ad, req_len) if a == merged))
+    L = T - tk
+    A, B = rand_lora(ranks, H, H, dtype, n_slots=4, seed=31, wstd=0.05)
+    a_start, a_len, a_loc, total = build_tables(ranks, 4, shuffle=True, contiguous_slots=True, seed=4)
+    key_buffer = fill_pool_a(A, ranks, a_start, a_loc, total, H, dtype).view(total, 8, H // 8).to(DEV)
+    value_buffer = fill_pool_b(B, ranks, a_start, a_loc, total, H, dtype, layout="rows").view(total, 8, H // 8).to(DEV)
+    ast_d, alen_d, aloc_d = t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV)
+    scaling = torch.ones(len(ranks), dtype=dtype, device=DEV)
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(T, H, generator=g).to(dtype)
+    slot = 1
+    W0 = (torch.randn(H, H, generator=g) * 0.02).to(dtype)
+    Wm = (W0.float() + A[slot][merged].float() @ B[slot][merged].float()).to(dtype)     # merged mode, scale 1
+    q0 = (x.float() @ Wm.float()).to(dtype)                                              # base projection
+    # problem table of the stacked rows: own adapters over [0, L), the merged one over [L, 2L)
+    tok2 = np.concatenate([tok[tk:], np.full(L, merged, np.int64)])
+    packer = ops.Packer(2 * L, len(ranks), DEV)
+    pk = packer.pack(torch.from_numpy(tok2).to(DEV), alen_d, sort=False)
+    P = pk.host_counts()["P"]
+    tables = (pk.seg_len, pk.seg_rank, pk.seg_adapter, pk.seg_start)
+    tmp_d = torch.zeros(60 * 128, dtype=torch.int8, device=DEV)
+    tiles = (64, 32, 32, 32, 32, 32)
+    bins = torch.from_numpy(tok2).to(DEV)
+    q = q0.to(DEV)
+    sub = x.to(DEV)[tk:]
+    stacked = torch.cat([sub, sub], dim=0)
+    delta = torch.zeros(2 * L, max_r, dtype=dtype, device=DEV)
+    out = torch.zeros(2 * L, H, dtype=dtype, device=DEV)
+    dispatch_sgmm(delta, stacked, key_buffer, ast_d, alen_d, aloc_d, bins, slot, scaling, *tables, tmp_d, P, *tiles)
+    torch.cuda.synchronize()
+    dispatch_sgmm(out, delta, value_buffer, ast_d, alen_d, aloc_d, bins, slot, scaling, *tables, tmp_d, P, *tiles)
+    q[tk:] += out[:L] - out[L:]
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    # each half against the restated operator, then the end result against base + own adapter in fp32
+    oc, rc, li, si = (v[:P + (1 if i == 3 else 0)].cpu().numpy() for i, v in enumerate(tables))
+    wa, wb = key_buffer.cpu().view(total, H), value_buffer.cpu().view(total, H)
+    v_ref = oracle.atmm_shrink_ref(torch.zeros(2 * L, max_r, dtype=dtype), stacked.cpu(), wa, a_start, a_loc, slot,
+                                   oc, rc, li, si, P)
+    assert _err(delta, v_ref) <= TOL
+    o_ref = oracle.atmm_expand_ref(torch.zeros(2 * L, H, dtype=dtype), v_ref.to(dtype), wb, a_start, a_loc, slot,
+                                   oc, rc, li, si, P)
+    assert _err(out, o_ref) <= TOL
+    want = x.float() @ W0.float()
+    for t in range(T):
+        a = int(tok[t])
+        want[t] += (x[t].float() @ A[slot][a].float()) @ B[slot][a].float()
+    assert torch.equal(q[:tk].cpu(), q0[:tk])                               # the merged adapter's rows are not touched
+    assert (q.cpu().float() - want).abs().max().item() <= 2e-2              # three roundings of a 16-bit q on the way
+
+
 # --------------------------------------------------------------------------- step (packed batch, many problems)
 def _step_case(ops, batch, proj_ids, layers=1, mma_min=16, gather_path="mma", wide_gather=None):
     from valora_b200.engine import LoraStepEngine
@@ -519,6 +587,59 @@ def test_step_from_host_buffers_matches_resident_step(ops, overlap):
                 assert torch.equal(out[l][p], want[l][p]), (l, p)
                 out[l][p].zero_()
     assert h2d == b.T * 8 + L * b.T * (512 + 512 + 512 + 1024) * 2 and d2h == L * b.T * (512 + 1024) * 2
+
+
+def test_step_shared_inputs_match_private_copies(ops):
+    """q/k/v-style groups: three projections that read ONE activation buffer give bit for
+    bit what three private copies of it give, resident and from host buffers (where the
+    shared X crosses the link once)."""
+    from valora_b200.engine import LoraStepEngine
+    b = workloads.config0()
+    projs = [("q", 512, 512), ("k", 512, 256), ("v", 512, 256), ("o", 512, 512), ("up", 512, 1024), ("gate", 512, 1024)]
+    input_of = [0, 0, 0, 3, 4, 4]
+    L = 2
+    shared = LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, L, b.T, input_of=input_of)
+    private = LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, L, b.T)
+    shared.randomize_weights(seed=6)
+    private.randomize_weights(seed=6)
+    assert shared.x[0][1] is shared.x[0][0] and shared.x[1][5] is shared.x[1][4] and shared.x[0][3] is not shared.x[0][0]
+    g = torch.Generator().manual_seed(10)
+    xh = [[torch.randn(b.T, hi, generator=g).to(b.dtype).pin_memory() for _, hi, _ in projs] for _ in range(L)]
+    yh = [[torch.randn(b.T, ho, generator=g).to(b.dtype).pin_memory() for _, _, ho in projs] for _ in range(L)]
+    for l in range(L):
+        for p in range(len(projs)):
+            private.x[l][p].copy_(xh[l][input_of[p]])
+            private.y[l][p].copy_(yh[l][p])
+            shared.y[l][p].copy_(yh[l][p])
+            if input_of[p] == p:
+                shared.x[l][p].copy_(xh[l][p])
+    tok = torch.from_numpy(b.tok_adapter.astype(np.int64)).to(DEV)
+    private.step(tok)
+    shared.step(tok)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    for l in range(L):
+        for p in range(len(projs)):
+            assert torch.equal(shared.y[l][p], private.y[l][p]), (l, p)
+    # oracle on one problem of a group
+    A, B = zip(*[private.adapter_weights(1, 2, a) for a in range(len(b.ranks))])
+    want = oracle.ragged_lora_ref_fp32(yh[1][2], xh[1][0], [a.cpu() for a in A], [bb.cpu() for bb in B],
+                                  b.req_len, b.req_adapter, b.scalings())
+    assert (shared.y[1][2].cpu().float() - want).abs().max().item() <= 1e-2
+    # from host buffers: entries of xh that are not a group's first are never read
+    out = [[torch.zeros(b.T, ho, dtype=b.dtype).pin_memory() for _, _, ho in projs] for _ in range(L)]
+    tok_h = torch.from_numpy(b.tok_adapter.astype(np.int64)).pin_memory()
+    tok_d = torch.empty(b.T, dtype=torch.int64, device=DEV)
+    h2d, d2h = shared.step_host(tok_h, xh, yh, tok_d, y_out_host=out)
+    torch.cuda.current_stream().synchronize()
+    for l in range(L):
+        for p in range(len(projs)):
+            assert torch.equal(out[l][p], private.y[l][p].cpu()), (l, p)
+    assert h2d == b.T * 8 + L * b.T * (3 * 512 + sum(ho for _, _, ho in projs)) * 2
+    with pytest.raises(ValueError):
+        LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, 1, b.T, input_of=[0, 0, 1, 3, 4, 4])
+    with pytest.raises(ValueError):
+        LoraStepEngine([("a", 512, 512), ("b", 256, 512)], b.ranks, b.scalings(), b.dtype, DEV, 1, b.T, input_of=[0, 0])
 
 
 @pytest.mark.parametrize("gather_path", ["mma", "simt"])

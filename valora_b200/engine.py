@@ -28,8 +28,14 @@ class LoraStepEngine:
                  scalings: Sequence[float], dtype, device, layers: int, max_tokens: int,
                  tile_m: int = 128, mma_min_rows: int = 16, gather_rows_per_tile: Optional[int] = None,
                  alloc_activations: bool = True, gather_path: str = "mma",
-                 wide_gather: Optional[bool] = None):
-        """gather_path: "mma" sends rows that are not consecutive in the batch (decode
+                 wide_gather: Optional[bool] = None, input_of: Optional[Sequence[int]] = None):
+        """input_of[p] = the projection whose activations projection p reads (itself by
+        default).  q, k and v of a transformer layer read the same rows, as do gate and
+        up (lora_unordered_batch_infer.py:946-965 passes one `input_embs` view to three
+        shrinks): with input_of = [0, 0, 0, 3, 4, 4, 6] the engine keeps one X per group,
+        the problems of a group point at it, and what the first of them brings in from
+        HBM the others find in L2.
+        gather_path: "mma" sends rows that are not consecutive in the batch (decode
         tokens) through the tensor-core kernels with gathered rows (up to 128 rows of
         an adapter per tile); "simt" sends them through the gather mat-vec kernels
         (8 rows per tile).  wide_gather: let a gather stage of the expand take as many
@@ -45,6 +51,14 @@ class LoraStepEngine:
         if gather_path == "mma" and gather_rows_per_tile > 16:
             raise ValueError("a gather tile on the tensor-core path holds at most 16 rows")
         self.projections = list(projections)
+        self.input_of = list(range(len(self.projections))) if input_of is None else [int(i) for i in input_of]
+        if len(self.input_of) != len(self.projections):
+            raise ValueError("input_of needs one entry per projection")
+        for p, src in enumerate(self.input_of):
+            if not (0 <= src <= p) or self.input_of[src] != src:
+                raise ValueError("input_of[p] must name p itself or an earlier projection that reads its own input")
+            if self.projections[src][1] != self.projections[p][1]:
+                raise ValueError("projections that share an input must have the same input width")
         self.ranks = [int(r) for r in ranks]
         self.dtype, self.device = dtype, torch.device(device)
         self.layers, self.max_tokens = int(layers), int(max_tokens)
@@ -77,8 +91,12 @@ class LoraStepEngine:
         self._copy_in = self._copy_out = None
         if alloc_activations:
             for _ in range(self.layers):
-                self.x.append([torch.zeros((self.max_tokens, hi), dtype=dtype, device=self.device)
-                               for _, hi, _ in self.projections])
+                xs: List[torch.Tensor] = []
+                for p, (_, hi, _) in enumerate(self.projections):
+                    src = self.input_of[p]
+                    xs.append(xs[src] if src != p else
+                              torch.zeros((self.max_tokens, hi), dtype=dtype, device=self.device))
+                self.x.append(xs)
                 self.y.append([torch.zeros((self.max_tokens, ho), dtype=dtype, device=self.device)
                                for _, _, ho in self.projections])
             self.build_plan()
@@ -198,9 +216,11 @@ class LoraStepEngine:
         for layer in range(self.layers):
             with torch.cuda.stream(s_in):
                 for p in range(n_proj):
-                    self.x[layer][p][:T].copy_(x_host[layer][p][:T], non_blocking=True)
+                    if self.input_of[p] == p:          # a shared input crosses the link once
+                        self.x[layer][p][:T].copy_(x_host[layer][p][:T], non_blocking=True)
+                        h2d += x_host[layer][p][:T].numel() * 2
                     self.y[layer][p][:T].copy_(y_host[layer][p][:T], non_blocking=True)
-                    h2d += (x_host[layer][p][:T].numel() + y_host[layer][p][:T].numel()) * 2
+                    h2d += y_host[layer][p][:T].numel() * 2
             if overlap:
                 cur.wait_stream(s_in)      # waits for what s_in holds now: this layer's inputs
                 self.plan.run(packed, self.scales, max_mma_tiles, max_gather_tiles, phase_mask=flags,

@@ -1,11 +1,13 @@
 """Micro-benchmarks on one B200, one JSON line each.
 
+    python -m valora_b200.microbench --config 0     # ragged shrink + expand drop-in call, fp16, 928 tokens in 6 segments
     python -m valora_b200.microbench --config 1     # decode BGMV drop-in call, bf16, 512 tokens
     python -m valora_b200.microbench --config 1 --api step   # the same decode batch through the step API
     python -m valora_b200.microbench --config 2     # prefill, mixed ranks 8..128, fp16, 7 projections (step API)
+    python -m valora_b200.microbench --config 3 --shared-x   # the mixed batch with q/k/v and up/gate reading one X each
     python -m valora_b200.microbench --config 4     # 16384 tokens, 1024 adapters, ranks 16..128, bf16 (step API)
 
-Config 1:  A measurement walks `--layers` independent copies
+Configs 0 and 1:  A measurement walks `--layers` independent copies
 of the operator's tensors (own pools, own activations; together larger than
 L2), one shrink and one expand call per copy, and times the walk with CUDA
 events on the launching stream; GB/s are algorithmic bytes (activations once,
@@ -142,20 +144,98 @@ def bench_bgmv(layers: int, reps: int, warmup: int, dev, eager: bool = False):
     }
 
 
-def bench_step(config: int, layers: int, reps: int, warmup: int, dev):
-    """Configs 2 and 4 through LoraStepEngine.step (device packer + one shrink and one
+def bench_atmm(layers: int, reps: int, warmup: int, dev, eager: bool = False):
+    """Config 0 through the 21-argument ragged call: shrink (4096 -> r) then expand
+    (r -> 4096) over the six segments, problem table in request order as the
+    reference's host packer would build it, adapter scale applied in the expand."""
+    b = workloads.config0()
+    H, n_ad, T = workloads.H, b.n_adapters, b.T
+    ranks = [int(r) for r in b.ranks]
+    max_r = max(ranks)
+    g = torch.Generator(device=dev)
+    g.manual_seed(b.seed)
+    pools_a = [AdapterPool(sum(ranks) + 16, H, 1, b.dtype, dev, 1) for _ in range(layers)]
+    pools_b = [AdapterPool(sum(ranks) + 16, H, 1, b.dtype, dev, 1) for _ in range(layers)]
+    for pools in (pools_a, pools_b):
+        for pool in pools:
+            for a in range(n_ad):
+                pool.load_adapter(f"a{a}", ranks[a], workloads.ALPHA / ranks[a], [[None]])
+            pool.buffer[0].copy_((torch.randn(pool.buffer[0].shape, generator=g, device=dev) * 0.02).to(b.dtype))
+    x = [torch.randn(T, H, generator=g, device=dev).to(b.dtype) for _ in range(layers)]
+    y = [torch.randn(T, H, generator=g, device=dev).to(b.dtype) for _ in range(layers)]
+    v = [torch.zeros(T, max_r, dtype=b.dtype, device=dev) for _ in range(layers)]
+    idx = torch.from_numpy(b.tok_adapter.astype(np.int64)).to(dev)
+    packer = ops.Packer(T, n_ad, dev)
+    pk = packer.pack(idx, pools_a[0].a_len, sort=False)
+    P = pk.host_counts()["P"]
+    tables = (pk.seg_len, pk.seg_rank, pk.seg_adapter, pk.seg_start)
+    scales = pools_a[0].a_scaling
+
+    def wview(pool):
+        return pool.buffer[0].view(pool.buffer[0].shape[0], 32, H // 32)
+
+    wa = [wview(p) for p in pools_a]
+    wb = [wview(p) for p in pools_b]
+
+    def shrink(l):
+        p = pools_a[l]
+        ops.atmm(v[l], x[l], wa[l], p.a_start, p.a_len, p.a_loc, idx, 0, scales, *tables, None, P)
+
+    def expand(l):
+        p = pools_b[l]
+        ops.atmm(y[l], v[l], wb[l], p.a_start, p.a_len, p.a_loc, idx, 0, scales, *tables, None, P, apply_scale=True)
+
+    e = 2
+    rt = int(b.ranks[b.touched()].sum())
+    lr = int(sum(int(l) * ranks[int(a)] for l, a in zip(b.req_len, b.req_adapter)))
+    bytes_shrink = (T * H + rt * H) * e + lr * e
+    bytes_expand = (2 * T * H + rt * H) * e + lr * e
+    ms_s = _time_walk(shrink, layers, reps, warmup, eager)
+    ms_e = _time_walk(expand, layers, reps, warmup, eager)
+    ms_b = _time_walk(lambda l: (shrink(l), expand(l)), layers, reps, warmup, eager)
+    if ops.device_status() != 0:
+        raise SystemExit("a bounded wait gave up inside a kernel")
+    peak, src = _peak()
+
+    def gbs(nbytes, ms):
+        return nbytes * layers / (ms * 1e-3) / 1e9
+
+    flops = 4 * H * lr
+    return {
+        "bench": "ragged_atmm_dropin", "workload": b.name, "dtype": "fp16", "tokens": T, "segments": int(P),
+        "adapters": n_ad, "ranks": ranks, "hidden": H, "layers_walked": layers,
+        "shrink": {"us_per_call": ms_s * 1e3 / layers, "gbs": gbs(bytes_shrink, ms_s),
+                   "frac": gbs(bytes_shrink, ms_s) / peak, "algorithmic_bytes": bytes_shrink},
+        "expand": {"us_per_call": ms_e * 1e3 / layers, "gbs": gbs(bytes_expand, ms_e),
+                   "frac": gbs(bytes_expand, ms_e) / peak, "algorithmic_bytes": bytes_expand},
+        "both": {"us_per_pair": ms_b * 1e3 / layers, "gbs": gbs(bytes_shrink + bytes_expand, ms_b),
+                 "frac": gbs(bytes_shrink + bytes_expand, ms_b) / peak,
+                 "tokens_per_s": T * layers / (ms_b * 1e-3), "tflops": flops * layers / (ms_b * 1e-3) / 1e12},
+        "peak_gbs": peak, "peak_source": src, "launch": "call by call" if eager else "one CUDA graph per walk, replayed",
+    }
+
+
+def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: bool = False):
+    """A config through LoraStepEngine.step (device packer + one shrink and one
     expand launch): `layers` copies of the config's projections, every copy with its
-    own pools and activations, CUDA events around each stage."""
+    own pools and activations, CUDA events around each stage.  shared_x: q/k/v and
+    up/gate of a copy read one X each (configs with the seven projections)."""
     from .engine import LoraStepEngine
     b = workloads.CONFIGS[config]()
     b.layers = layers
-    eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T)
+    input_of = None
+    if shared_x:
+        if len(b.projections) != len(workloads.SHARED_INPUT_OF):
+            raise SystemExit("--shared-x needs a config with the seven projections (2 or 3)")
+        input_of = list(workloads.SHARED_INPUT_OF)
+    eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T, input_of=input_of)
     eng.randomize_weights(seed=b.seed)
     g = torch.Generator(device=dev)
     g.manual_seed(b.seed)
     for l in range(layers):
         for p in range(len(b.projections)):
-            eng.x[l][p].normal_(generator=g)
+            if eng.input_of[p] == p:
+                eng.x[l][p].normal_(generator=g)
             eng.y[l][p].normal_(generator=g)
     tok = torch.from_numpy(b.tok_adapter.astype(np.int64)).to(dev)
     for _ in range(warmup):
@@ -176,9 +256,9 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev):
         raise SystemExit("a bounded wait gave up inside a kernel")
     peak, src = _peak()
     step_ms = float(np.median(tot))
-    nbytes, flops = b.algorithmic_bytes(), b.algorithmic_flops()
+    nbytes, flops = b.algorithmic_bytes(input_of), b.algorithmic_flops()
     return {
-        "bench": "lora_step", "workload": b.name, "dtype": str(b.dtype).replace("torch.", ""), "tokens": b.T,
+        "bench": "lora_step", "shared_x": bool(shared_x), "workload": b.name, "dtype": str(b.dtype).replace("torch.", ""), "tokens": b.T,
         "adapters": b.n_adapters, "adapters_touched": int(len(b.touched())),
         "ranks": sorted(set(int(r) for r in b.ranks)), "projections": len(b.projections), "layers": layers,
         "mma_tiles": counts["n_mma"], "gather_tiles": counts["n_gather"],
@@ -191,23 +271,28 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 4])
-    ap.add_argument("--layers", type=int, default=0, help="independent copies walked (default: 32 / 4 / 8)")
+    ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4])
+    ap.add_argument("--layers", type=int, default=0, help="independent copies walked (default: 32 / 4 / 32 / 8)")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--eager", action="store_true", help="launch call by call (no CUDA graph), for profilers")
     ap.add_argument("--api", default="auto", choices=["auto", "dropin", "step"],
                     help="config 1 only: the 9-argument decode call (default) or the step API")
+    ap.add_argument("--shared-x", action="store_true",
+                    help="step API, configs 2 and 3: q/k/v and up/gate read one X per copy")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    if args.config == 1 and args.api != "step":
+    if args.config == 0:
+        print(json.dumps(bench_atmm(args.layers or 32, args.reps, args.warmup, dev, args.eager)))
+    elif args.config == 1 and args.api != "step":
         print(json.dumps(bench_bgmv(args.layers or 32, args.reps, args.warmup, dev, args.eager)))
     else:
-        default_layers = {1: 32, 2: 4, 4: 8}[args.config]
-        print(json.dumps(bench_step(args.config, args.layers or default_layers, args.reps, args.warmup, dev)))
+        default_layers = {1: 32, 2: 4, 3: 32, 4: 8}[args.config]
+        print(json.dumps(bench_step(args.config, args.layers or default_layers, args.reps, args.warmup, dev,
+                                    args.shared_x)))
 
 
 if __name__ == "__main__":

@@ -22,6 +22,9 @@ PROJECTIONS: List[Tuple[str, int, int]] = [
     ("q", H, H), ("k", H, H), ("v", H, H), ("o", H, H),
     ("up", H, F), ("gate", H, F), ("down", F, H),
 ]
+# which projection's activations each projection reads when a caller shares them:
+# q, k, v read the layer input, up and gate the MLP input
+SHARED_INPUT_OF: List[int] = [0, 0, 0, 3, 4, 4, 6]
 ALPHA = 16.0
 
 
@@ -65,10 +68,12 @@ class Batch:
         per = sum(hi + ho for _, hi, ho in self.projections)
         return 2 * lr * per * self.layers
 
-    def algorithmic_bytes(self) -> int:
-        """X once, Y0 read + Y write, each touched adapter weight once (2-byte elements)."""
+    def algorithmic_bytes(self, input_of=None) -> int:
+        """X once, Y0 read + Y write, each touched adapter weight once (2-byte elements).
+        input_of: projections that read another projection's X do not count it again."""
         e = 2
-        act = sum(self.T * hi + 2 * self.T * ho for _, hi, ho in self.projections) * e
+        act = sum((self.T * hi if input_of is None or input_of[p] == p else 0) + 2 * self.T * ho
+                  for p, (_, hi, ho) in enumerate(self.projections)) * e
         rt = int(self.ranks[self.touched()].astype(np.int64).sum())
         wts = rt * sum(hi + ho for _, hi, ho in self.projections) * e
         return (act + wts) * self.layers
