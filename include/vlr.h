@@ -50,6 +50,9 @@ extern "C" {
                                         atmm/valora/csrc/bgmv/bgmv_impl.cuh:174); default overwrites */
 #define VLR_ATMM_APPLY_SCALE 2       /* expand multiplies by lora_scales[adapter]; the reference
                                         epilogue uses alpha = 1 (same file :174, :236) */
+#define VLR_ATMM_FULL_TILES 4        /* shrink: always cut segments into 128-row tiles.  Without it a
+                                        call with few rows (T/128 + num_problems <= half the SMs) uses
+                                        32-row tiles: more CTAs, each walking K in fewer, fuller stages */
 
 /* kinds in the tile schedule written by vlr_pack */
 #define VLR_TILE_MMA 0

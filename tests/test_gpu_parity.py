@@ -241,16 +241,20 @@ def _atmm_case(ops, dtype, ranks, seg_len, seg_ad, h, qkvo=0, n_slots=1, seed=0,
     scales = torch.tensor([16.0 / r for r in ranks]).to(dtype)
     dev = lambda t: t.to(DEV)
     args_tail = (t64(oc, DEV), t64(rc, DEV), t64(li, DEV), t64(si, DEV), None, P)
-    v = dev(v0)
-    ops.atmm(v, dev(x), dev(wa).view(total, 1, h), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
-             dev(idx), qkvo, dev(scales), *args_tail)
-    torch.cuda.synchronize()
-    assert ops.device_status() == 0
-    assert _err(v, ref_v) <= TOL
-    # columns >= rank of each segment are untouched
-    vc = v.cpu().float()
-    for s in range(P):
-        assert torch.all(vc[si[s]:si[s + 1], rc[s]:] == poison)
+    outs = []
+    for full_tiles in (False, True):         # 32-row tiles (what a call with few rows gets) and 128-row tiles
+        v = dev(v0)
+        ops.atmm(v, dev(x), dev(wa).view(total, 1, h), t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV),
+                 dev(idx), qkvo, dev(scales), *args_tail, full_tiles=full_tiles)
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        assert _err(v, ref_v) <= TOL
+        # columns >= rank of each segment are untouched
+        vc = v.cpu().float()
+        for s in range(P):
+            assert torch.all(vc[si[s]:si[s + 1], rc[s]:] == poison)
+        outs.append(v.cpu())
+    assert torch.equal(outs[0], outs[1])     # same K order, same fp32 accumulation: the cut does not change a bit
     vin = ref_v.to(dtype)
     ref_y = oracle.atmm_expand_ref(y0, vin, wb, a_start, a_loc, qkvo, oc, rc, li, si, P, scales=scales)
     y = dev(y0)

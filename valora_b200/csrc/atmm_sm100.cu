@@ -122,11 +122,12 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
     ti.rows = t[4];
   } else {
     const int b = (int)tb;
+    const int tm = (!expand && src.tile_rows > 0) ? src.tile_rows : kTileM;
     int base = 0;
     for (int64_t p0 = 0; p0 < src.num_problems; p0 += 32) {
       const int64_t p = p0 + lane;
       const int m = p < src.num_problems ? (int)src.output_counts[p] : 0;
-      const int nt = m > 0 ? (m + kTileM - 1) / kTileM : 0;
+      const int nt = m > 0 ? (m + tm - 1) / tm : 0;
       int inc = nt;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -138,13 +139,13 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
       const unsigned who = __ballot_sync(0xffffffffu, mine);
       if (who) {
         const int srcl = __ffs(who) - 1;
-        const int m0 = (b - __shfl_sync(0xffffffffu, excl, srcl)) * kTileM;
+        const int m0 = (b - __shfl_sync(0xffffffffu, excl, srcl)) * tm;
         const int64_t pp = p0 + srcl;
         ti.valid = 1;
         ti.adapter = (int)src.lora_ids[pp];
         ti.rank = (int)src.rank_counts[pp];
         ti.row0 = (int)src.start_ids[pp] + m0;
-        ti.rows = min(kTileM, (int)src.output_counts[pp] - m0);
+        ti.rows = min(tm, (int)src.output_counts[pp] - m0);
         break;
       }
       base += __shfl_sync(0xffffffffu, inc, 31);
@@ -457,7 +458,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         if (ok) tc_fence_after();
         const SubLayout sl = sub_layout(ti, n_pad, stage_bytes);
         const int nstages = (kblocks + sl.kbs - 1) / sl.kbs;
-        uint32_t ks = 0;                               // K slices of this tile issued so far
+        uint32_t aoff = 0, first = (uint32_t)nacc;     // next accumulator chain; chains not yet started
         for (int st = 0; st < nstages && ok; ++st, ++kiter) {
           const int s = kiter % nst;
           ok = mbar_wait(full_bar(s), (kiter / nst) & 1, &abort_s);
@@ -465,14 +466,22 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
           trace_stamp(src, kiter, 1);
           tc_fence_after();
           const int nsub = min(sl.kbs, kblocks - st * sl.kbs);
+          // One thread issues at most one MMA per 55-60 cycles, and with N <= 64 that, not the
+          // tensor pipe (about 48 cycles), is what a short tile's 256 MMAs cost: so nothing but
+          // additions per instruction.  The address field of a descriptor counts 16-byte units:
+          // + 2 per 16-column K slice, + sub / 16 per K block.
+          uint64_t ad = smem_desc_sw128(x_stage(s), 16, 1024);
+          uint64_t bd = smem_desc_sw128(x_stage(s) + sl.xbytes, 16, 1024);
+          const uint64_t dstep = (uint64_t)(sl.sub >> 4);
           for (int j = 0; j < nsub; ++j) {
-            const uint32_t sb = x_stage(s) + j * sl.sub;
 #pragma unroll
-            for (int k = 0; k < kBoxCols / 16; ++k, ++ks) {
-              const uint64_t ad = smem_desc_sw128(sb + k * 32, 16, 1024);
-              const uint64_t bd = smem_desc_sw128(sb + sl.xbytes + k * 32, 16, 1024);
-              umma_f16(tacc + (ks & (nacc - 1)) * astr, ad, bd, idesc, ks >= (uint32_t)nacc);
+            for (int k = 0; k < kBoxCols / 16; ++k) {
+              umma_f16(tacc + aoff, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc, first == 0);
+              aoff = (aoff + (uint32_t)astr) & 255u;
+              first = first > 0 ? first - 1 : 0;
             }
+            ad += dstep;
+            bd += dstep;
           }
           umma_commit(empty_bar(s));
           trace_stamp(src, kiter, 2);
@@ -1208,8 +1217,13 @@ extern "C" int vlr_atmm(void* y, const void* x, const void* w, const int64_t* a_
   src.a_loc = a_loc;
   src.slot = qkvo;
   src.mode = 0;
-  // every problem with m rows has ceil(m/128) tiles; sum <= T/128 + num_problems
-  const int64_t max_tiles = T / kTileM + num_problems;
+  // every problem with m rows has ceil(m / tile rows) tiles; sum <= T / tile rows + num_problems.
+  // A shrink with few rows is a few CTAs each walking all of K at the latency of a stage; cut
+  // into 32-row tiles it occupies four times as many SMs, and a stage holds several K blocks.
+  src.tile_rows = kTileM;
+  if (!expand && !(flags & VLR_ATMM_FULL_TILES) && T / kTileM + num_problems <= sm_count() / 2)
+    src.tile_rows = 32;
+  const int64_t max_tiles = T / src.tile_rows + num_problems;
   return atmm_launch(y, x, w, lora_scales, src, max_tiles, T, (int)h_in, (int)h_out, w_cells, dtype,
                      flags, (cudaStream_t)stream, 1);
 }

@@ -92,6 +92,7 @@ struct TileSource {
   unsigned int* item_counter;
   // work decomposition, filled by the launcher
   int64_t max_tiles;                 // mode 0: upper bound of the tile count
+  int tile_rows;                     // mode 0, shrink: rows per tile (32 or 128; 0 = 128)
   int n_problems;
   int nsplit;                        // expand: work items per tile (column shares)
   // operand rings, sized by the launcher from the largest rank the launch may meet

@@ -14,7 +14,7 @@ from . import _lib
 
 F16, BF16 = 0, 1
 LAYOUT_PUNICA, LAYOUT_ROWS = 0, 1
-ATMM_ACCUMULATE_SHRINK, ATMM_APPLY_SCALE = 1, 2
+ATMM_ACCUMULATE_SHRINK, ATMM_APPLY_SCALE, ATMM_FULL_TILES = 1, 2, 4
 TILE_INTS, COUNT_INTS = 8, 8
 MAX_RANK = 128
 PHASE_SHRINK_MMA, PHASE_SHRINK_GATHER, PHASE_EXPAND_MMA, PHASE_EXPAND_GATHER, PHASE_ALL = 1, 2, 4, 8, 15
@@ -106,11 +106,12 @@ def bgmv(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies, qkvo, lora
 def atmm(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies, qkvo, lora_scales,
          output_counts, rank_counts, lora_ids, start_ids, tmp_d, num_problems,
          thrd_x=0, thrd_y=0, thrd_z=0, wrap_x=0, wrap_y=0, wrap_z=0, *,
-         accumulate_shrink: bool = False, apply_scale: bool = False):
+         accumulate_shrink: bool = False, apply_scale: bool = False, full_tiles: bool = False):
     """Ragged grouped shrink / expand; argument meaning and checks of
     atmm_ops.dispatch_bgmv (atmm/valora/csrc/lora_ops.cc:115-186).  The six tile
     integers are accepted and ignored (tile shapes are chosen on the device side
-    for sm_100a)."""
+    for sm_100a).  full_tiles: keep 128-row tiles in a shrink with few rows, which
+    by default is cut into 32-row tiles."""
     _common_checks(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies)
     for t, n in ((output_counts, "output_counts"), (rank_counts, "rank_counts"),
                  (lora_ids, "lora_ids"), (start_ids, "start_ids")):
@@ -125,7 +126,8 @@ def atmm(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies, qkvo, lora
     wide = max(h_in, h_out)
     if w.size(1) * w.size(2) != wide:
         raise RuntimeError(f"No suitable kernel. h_in={h_in} h_out={h_out} dtype={x.dtype}")
-    flags = (ATMM_ACCUMULATE_SHRINK if accumulate_shrink else 0) | (ATMM_APPLY_SCALE if apply_scale else 0)
+    flags = ((ATMM_ACCUMULATE_SHRINK if accumulate_shrink else 0) | (ATMM_APPLY_SCALE if apply_scale else 0)
+             | (ATMM_FULL_TILES if full_tiles else 0))
     if apply_scale:
         _check_input(lora_scales, "lora_scales")
     lib = _bind(x.device)
