@@ -5,6 +5,7 @@
     python -m valora_b200.microbench --config 1 --api step   # the same decode batch through the step API
     python -m valora_b200.microbench --config 2     # prefill, mixed ranks 8..128, fp16, 7 projections (step API)
     python -m valora_b200.microbench --config 3 --shared-x   # the mixed batch with q/k/v and up/gate reading one X each
+    python -m valora_b200.microbench --config 3 --trace expand   # stage timing of one launch (clock64 stamps of CTA 0)
     python -m valora_b200.microbench --config 4     # 16384 tokens, 1024 adapters, ranks 16..128, bf16 (step API)
 
 Configs 0 and 1:  A measurement walks `--layers` independent copies
@@ -269,6 +270,58 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
     }
 
 
+def trace_step(config: int, layers: int, phase: str, dev):
+    """Stage timing of CTA 0 of one shrink or expand launch (clock64 stamps the kernels
+    write while a trace buffer is set): medians over the stages of issue -> operands seen
+    by the MMA thread -> epilogue / MMAs issued -> stage handed back, in cycles."""
+    import ctypes
+    from . import _lib
+    from .engine import LoraStepEngine
+    lib = _lib.load()
+    b = workloads.CONFIGS[config]()
+    b.layers = layers
+    eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T)
+    eng.randomize_weights(seed=b.seed)
+    for l in range(layers):
+        for p in range(len(b.projections)):
+            eng.x[l][p].normal_()
+            eng.y[l][p].normal_()
+    tok = torch.from_numpy(b.tok_adapter.astype(np.int64)).to(dev)
+    for _ in range(3):
+        packed = eng.step(tok)
+    torch.cuda.synchronize()
+    cap = 1 << 16
+    buf = torch.zeros(cap * 8, dtype=torch.int64, device=dev)
+    bit = ops.PHASE_SHRINK_MMA if phase == "shrink" else ops.PHASE_EXPAND_MMA
+    lib.vlr_debug_set_trace(ctypes.c_void_p(buf.data_ptr()), cap * 8)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    eng.plan.run(packed, eng.scales, 0, 0, phase_mask=bit | eng._gather_flag(), max_rank=max(eng.ranks))
+    e1.record()
+    torch.cuda.synchronize()
+    lib.vlr_debug_set_trace(ctypes.c_void_p(0), 0)
+    t = buf.cpu().numpy().reshape(cap, 8)
+    n = int((t[:, 0] > 0).sum())
+    t = t[:n]
+
+    def med(a, c):
+        return int(np.median(t[1:, a] - t[1:, c])) if n > 1 else 0
+
+    out = {"bench": "stage_trace", "workload": b.name, "layers": layers, "phase": phase,
+           "kernel_us": e0.elapsed_time(e1) * 1e3, "stages_of_cta0": n,
+           "cycles_per_stage": float(t[:, 0].max() - t[:, 0].min()) / max(n - 1, 1),
+           "issue_interval_median": int(np.median(np.diff(t[:, 0]))) if n > 1 else 0,
+           "issue_to_operands_seen_median": med(1, 0)}
+    if phase == "shrink":
+        out["operands_seen_to_mmas_issued_median"] = med(2, 1)
+        out["copies_issued_median"] = med(3, 0)
+    else:
+        out["operands_seen_to_epilogue_start_median"] = med(2, 1)
+        out["epilogue_median"] = med(3, 2)
+        out["issue_to_handed_back_median"] = med(3, 0)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4])
@@ -280,12 +333,17 @@ def main():
                     help="config 1 only: the 9-argument decode call (default) or the step API")
     ap.add_argument("--shared-x", action="store_true",
                     help="step API, configs 2 and 3: q/k/v and up/gate read one X per copy")
+    ap.add_argument("--trace", choices=["shrink", "expand"],
+                    help="step API: print the stage timing of CTA 0 of one launch instead of timing steps")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    if args.config == 0:
+    if args.trace:
+        default_layers = {0: 1, 1: 4, 2: 2, 3: 4, 4: 2}[args.config]
+        print(json.dumps(trace_step(args.config, args.layers or default_layers, args.trace, dev)))
+    elif args.config == 0:
         print(json.dumps(bench_atmm(args.layers or 32, args.reps, args.warmup, dev, args.eager)))
     elif args.config == 1 and args.api != "step":
         print(json.dumps(bench_bgmv(args.layers or 32, args.reps, args.warmup, dev, args.eager)))
