@@ -293,6 +293,13 @@ def test_atmm_config0(ops):
                                      b.req_adapter.tolist(), 4096, seed=0)
 
 
+def test_atmm_widths_off_the_box_grid(ops):
+    """hidden sizes that are multiples of 8 but not of the 64-column box (the copy engine
+    zero-fills the ragged last K block / the last output block is stored in part)"""
+    for h in (72, 520, 1096):
+        _atmm_case(ops, torch.bfloat16, [16, 64, 8], [5, 140, 33, 1], [0, 1, 2, 1], h, seed=h)
+
+
 def test_atmm_legacy_accumulate_and_empty(ops):
     dtype, h, ranks = torch.float16, 256, [16]
     A, B = rand_lora(ranks, h, h, dtype, seed=9)
@@ -644,6 +651,59 @@ def test_step_shared_inputs_match_private_copies(ops):
         LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, 1, b.T, input_of=[0, 0, 1, 3, 4, 4])
     with pytest.raises(ValueError):
         LoraStepEngine([("a", 512, 512), ("b", 256, 512)], b.ranks, b.scalings(), b.dtype, DEV, 1, b.T, input_of=[0, 0])
+
+
+def test_step_replays_from_a_cuda_graph(ops):
+    """packer + shrink + expand captured once, replayed on batches whose token -> adapter
+    map changes between replays: the schedule is rebuilt on the device inside the graph,
+    so every replay must equal an eager step on the same inputs, bit for bit."""
+    from valora_b200.engine import LoraStepEngine
+    b = workloads.config3(layers=1)
+    projs = [("q", 1024, 1024), ("up", 1024, 2048)]
+    L = 2
+    eng = LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, L, b.T)
+    eng.randomize_weights(seed=12)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(13)
+    x0 = [[torch.randn(b.T, hi, generator=g, device=DEV).to(b.dtype) for _, hi, _ in projs] for _ in range(L)]
+    y0 = [[torch.randn(b.T, ho, generator=g, device=DEV).to(b.dtype) for _, _, ho in projs] for _ in range(L)]
+
+    def reset():
+        for l in range(L):
+            for p in range(len(projs)):
+                eng.x[l][p].copy_(x0[l][p])
+                eng.y[l][p].copy_(y0[l][p])
+
+    rng = np.random.default_rng(5)
+    toks = [b.tok_adapter.astype(np.int64)]
+    toks.append(np.roll(toks[0], 777))                                   # other rows become the decode rows
+    toks.append(rng.integers(0, b.n_adapters, size=b.T).astype(np.int64))  # no consecutive runs at all
+    tok_buf = torch.from_numpy(toks[0]).to(DEV)
+    eager = []
+    for t in toks:
+        reset()
+        tok_buf.copy_(torch.from_numpy(t))
+        eng.step(tok_buf)
+        torch.cuda.synchronize()
+        eager.append([[eng.y[l][p].clone() for p in range(len(projs))] for l in range(L)])
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        eng.step(tok_buf)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        eng.step(tok_buf)
+    for i in (2, 0, 1, 1):
+        reset()
+        tok_buf.copy_(torch.from_numpy(toks[i]))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        for l in range(L):
+            for p in range(len(projs)):
+                assert torch.equal(eng.y[l][p], eager[i][l][p]), (i, l, p)
 
 
 @pytest.mark.parametrize("gather_path", ["mma", "simt"])
