@@ -1101,7 +1101,11 @@ template <typename T>
 static int launch_atmm(void* y, const void* x, const void* w, const void* scales, TileSource src,
                        int64_t max_tiles, int64_t T_rows, int h_in, int h_out, int64_t w_cells,
                        int dtype, int flags, cudaStream_t stream, int n_problems) {
-  static bool attr_done = false;
+  // the shared-memory opt-in is per device: one flag per device this process has launched on
+  static bool attr_done_dev[64];
+  int cur_dev = 0;
+  if (cudaGetDevice(&cur_dev) != cudaSuccess || cur_dev < 0 || cur_dev >= 64) return VLR_ERR_RANGE;
+  bool& attr_done = attr_done_dev[cur_dev];
   if (!attr_done) {
     cudaError_t e = cudaSuccess;
     auto set = [&](const void* f, int bytes) {

@@ -848,7 +848,11 @@ int bgmv_decode_launch(void* y, const void* x, const void* w, const void* scales
                        const int64_t* indicies, int64_t batch, const int64_t* a_start,
                        const int64_t* a_len, const int64_t* a_loc, int64_t qkvo, int h_in, int h_out,
                        int dtype, cudaStream_t stream) {
-  static bool attr_done = false;
+  // the shared-memory opt-in is per device: one flag per device this process has launched on
+  static bool attr_done_dev[64];
+  int cur_dev = 0;
+  if (cudaGetDevice(&cur_dev) != cudaSuccess || cur_dev < 0 || cur_dev >= 64) return VLR_ERR_RANGE;
+  bool& attr_done = attr_done_dev[cur_dev];
   if (!attr_done) {
     cudaError_t e = cudaSuccess;
     auto set = [&](const void* f, int bytes) {
