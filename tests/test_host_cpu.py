@@ -63,6 +63,10 @@ def test_workloads_are_deterministic_and_shaped():
     assert c1.T == 512 and c1.algorithmic_flops() == 536_870_912
     c3 = workloads.config3()
     assert c3.n_prefill_req == 8 and (c3.req_len[8:] == 1).all() and len(c3.req_len) == 392
+    # shared activations: q/k/v and up/gate count their X once (three X tiles of 4096 columns fewer per layer)
+    shared = c3.algorithmic_bytes(workloads.SHARED_INPUT_OF)
+    assert c3.algorithmic_bytes() - shared == 3 * c3.T * 4096 * 2 * c3.layers
+    assert c3.algorithmic_bytes(list(range(7))) == c3.algorithmic_bytes()
     c4 = workloads.config4()
     assert c4.T == 16384 and int((c4.req_len > 1).sum()) == c4.n_prefill_req
     # adapter-group sharding covers the whole box batch exactly once
