@@ -2,11 +2,14 @@
  * libvlr - C ABI of the B200 (sm_100a) multi-LoRA batching operator.
  *
  * Plain pointers and sizes only.  Every pointer named "device" must be device
- * memory of the current CUDA device; the library allocates nothing and keeps
- * no state between calls except a cached driver entry point for tensor-map
- * encoding.  All work is enqueued on the stream passed in (a cudaStream_t cast
- * to void*; NULL = the legacy default stream) and the calls return without
- * synchronising.
+ * memory of the CURRENT CUDA device of the calling thread, and the stream must
+ * belong to it (vlr_set_device binds a thread).  The library allocates no
+ * device memory.  State it keeps between calls: a cached driver entry point
+ * for tensor-map encoding, per-device flags for kernel attributes, the
+ * process-wide device status word (vlr_device_status), and the per-device
+ * address of the built-in scratch of vlr_pack_static.  All work is enqueued on
+ * the stream passed in (a cudaStream_t cast to void*; NULL = the legacy default
+ * stream) and the calls return without synchronising.
  *
  * Return value: 0 on success, a negative VLR_ERR_* code when host-side argument
  * validation fails (nothing was launched), or a positive cudaError_t value
@@ -64,7 +67,8 @@ extern "C" {
 #define VLR_COUNT_MMA_TILES 1
 #define VLR_COUNT_GATHER_TILES 2
 #define VLR_COUNT_GATHER_ROWS 3
-#define VLR_COUNT_STATUS 4     /* 0 ok, 1 an adapter id was out of range, 2 tile capacity exceeded */
+#define VLR_COUNT_STATUS 4     /* 0 ok, 1 an adapter id was out of range (served as adapter 0),
+                                  2 tile capacity exceeded */
 #define VLR_COUNT_INTS 8
 
 int vlr_version(void);
@@ -131,6 +135,8 @@ int vlr_atmm(void* y, const void* x, const void* w,
  * rows in gather_rows.  counts[VLR_COUNT_INTS] receives the totals.
  * Capacities: perm, gather_rows: T; seg_*: min(T, n_adapters or T) + 1;
  * tiles: tiles_cap tiles of VLR_TILE_INTS int32.
+ * Limits: tile_m <= 128 (one MMA tile), gather_rows_per_tile <= 16, else
+ * VLR_ERR_RANGE.  Four small launches; counts is written in full every call.
  */
 size_t vlr_pack_workspace_bytes(int64_t T, int64_t n_adapters);
 int vlr_pack(const int64_t* tok_adapter, int64_t T, const int64_t* a_len, int64_t n_adapters,
@@ -140,9 +146,9 @@ int vlr_pack(const int64_t* tok_adapter, int64_t T, const int64_t* a_len, int64_
              int32_t* counts, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
- * vlr_pack with no scratch argument.  No counterpart in the reference (its
- * host packer allocates fresh CUDA tensors on every forward,
- * valora/server/router/req_queue.py:35-42).
+ * vlr_pack with no scratch argument.  No counterpart in the reference (there
+ * the metadata buffers are module-level CUDA tensors that reset_sgmm re-creates
+ * for every forward, valora/server/router/req_queue.py:35-42).
  *
  * For callers that cannot supply device scratch: a step that runs after the
  * serving pool has claimed the GPU's remaining memory, or host code behind an
@@ -171,19 +177,27 @@ int vlr_pack_static(const int64_t* tok_adapter, int64_t T, const int64_t* a_len,
 int vlr_var_len_copy(const int64_t* old_start, const int64_t* len, const int64_t* old_loc,
                      const int64_t* new_start, int64_t* new_loc, int64_t n, void* stream);
 
-/* Debug aid.  While a device buffer of n_int64 int64 is set, CTA 0 of the
- * tensor-core kernels stamps clock64 into it, 8 values per pipeline stage
- * (0 stage issued, 1 operands seen by the MMA thread, 2 MMAs issued or epilogue
- * started, 3 stage released, 4-7 points inside the epilogue).  NULL switches it off. */
-int vlr_debug_set_trace(void* dev_buffer, int64_t n_int64);
-
 /* Bind the calling thread's CUDA runtime state to a device (cudaSetDevice). */
 int vlr_set_device(int device);
 
-/* Device-side status word: 0 ok, 1 a bounded wait inside a tensor-core kernel
- * gave up (the kernel returned early and its output is incomplete).
- * Synchronises the device.  reset != 0 clears it. */
+/* Process-wide device status word, a bit set: 1 a bounded wait inside a kernel
+ * gave up (the kernel returned early and its output is incomplete), 2 a tile
+ * record was outside what its launch supports and was skipped (rank above the
+ * launch's max_rank or not a multiple of 8, too many rows).  0 = ok.
+ * Synchronises the device.  reset != 0 clears it.  vlr_lora_step can be given
+ * a status word of its own instead (dev_status), which the caller reads when
+ * and how it likes (no synchronisation here, usable under stream capture). */
 int vlr_device_status(int reset);
+
+/* Self-test of the bounded waits: one thread waits on a barrier nothing ever
+ * completes, gives up after budget_cycles (1 .. 2e9) and raises status bit 1 in
+ * *dev_status (NULL: the process-wide word).  dev_waited_cycles (may be NULL)
+ * receives the cycles the wait took.  The kernel returns normally; nothing
+ * faults and the context stays usable.  No counterpart in the reference, whose
+ * kernels have no waits of this kind and whose launch failures are printed and
+ * swallowed (atmm/valora/csrc/bgmv/bgmv_impl.cuh:185-198). */
+int vlr_selftest_bounded_wait(int64_t budget_cycles, int32_t* dev_status,
+                              int64_t* dev_waited_cycles, void* stream);
 
 /*
  * One step over many projections: shrink then expand of every (layer, projection)
@@ -237,6 +251,9 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
  * exceeds the bound are skipped.
  * phase_mask: which of the four launches to enqueue (VLR_PHASE_ALL for a step;
  * single phases let a harness time each kernel on its own).
+ * dev_status: device int32 the step's kernels OR their status bits into (see
+ * vlr_device_status for the bits), or NULL for the process-wide word.  The
+ * caller clears it and reads it (e.g. with the step's results).
  */
 #define VLR_PHASE_SHRINK_MMA 1
 #define VLR_PHASE_SHRINK_GATHER 2
@@ -259,7 +276,7 @@ int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
                   const int32_t* counts, const void* scales, int max_h_in, int max_h_out,
                   int max_rank, int dtype, int phase_mask, void* workspace, size_t workspace_bytes,
-                  void* stream);
+                  int32_t* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

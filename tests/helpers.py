@@ -85,3 +85,16 @@ def out_tolerance(ref32, dtype, tol=1e-2):
     mag = ref32.abs().clamp_min(1e-30)
     half_ulp = torch.exp2(torch.floor(torch.log2(mag)) - prec)
     return torch.maximum(torch.full_like(ref32, tol), half_ulp * 1.01 + 1e-4)
+
+
+def own_error(got, ref32):
+    """The kernel's own error, with the output grid taken out: the largest
+    |got - ref32| - half_ulp(ref32) over the elements (0 if none is positive).
+    What is left is accumulation order and the 16-bit rounding of the shrink
+    result between the two kernels, not the final rounding to the output type."""
+    if got.numel() == 0:
+        return 0.0
+    prec = 8 if got.dtype == torch.bfloat16 else 11
+    mag = ref32.abs().clamp_min(1e-30)
+    half_ulp = torch.exp2(torch.floor(torch.log2(mag)) - prec)
+    return float(((got.float().cpu() - ref32).abs() - half_ulp).clamp_min(0).max())

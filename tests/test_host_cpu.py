@@ -40,7 +40,15 @@ def test_host_validation_codes_without_a_gpu():
     assert lib.vlr_pack(one, 10, one, 8, 1, 128, 16, 8, one, one, one, one, one, one, 10, one, one,
                         one, 16, null) == -5                                                    # workspace too small
     assert lib.vlr_step_plan_bytes(3) == 3 * lib.vlr_step_plan_bytes(1) > 0
-    assert lib.vlr_lora_step(null, 2, 10, null, null, 0, 0, null, null, 4096, 4096, 64, 0, 15, null, 0, null) == -1
+    assert lib.vlr_lora_step(null, 2, 10, null, null, 0, 0, null, null, 4096, 4096, 64, 0, 15, null, 0, null,
+                             null) == -1
+    assert lib.vlr_pack(one, 10, one, 8, 1, 256, 16, 8, one, one, one, one, one, one, 10, one, one,
+                        one, 1 << 20, null) == -6                                               # tile_m > 128
+    assert lib.vlr_pack_static(one, 10, one, 8, 1, 128, 16, 32, one, one, one, one, one, one, 10, one, one,
+                               null) == -6                                                      # 32 gathered rows per tile
+    assert lib.vlr_pack_static(one, 9000, one, 8, 1, 128, 16, 8, one, one, one, one, one, one, 10, one, one,
+                               null) == -9                                                      # beyond the built-in scratch
+    assert lib.vlr_selftest_bounded_wait(0, null, null, null) == -6
     assert b"workspace" in lib.vlr_error_string(-5)
 
 

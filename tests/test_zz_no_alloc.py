@@ -50,12 +50,35 @@ def test_pack_static_matches_pack_on_two_calls_in_a_row():
         assert ref["counts"][4] == 0 and got["counts"][4] == 0
         for k in ref:
             assert np.array_equal(ref[k], got[k]), k
-    # and once more in reference order on the first batch (scratch now holds the second batch's bytes)
-    packer, tok_d, a_len, T = results[0]
-    got = _outputs(ops.pack_static(packer, tok_d, a_len, sort=False), T)
-    ref = _outputs(packer.pack(tok_d, a_len, sort=False), T)
-    for k in ref:
-        assert np.array_equal(ref[k], got[k]), k
+    # and once more in reference order on both batches (scratch holds the other batch's bytes
+    # each time; the second is at the limits).  Device memory in use must not move across these
+    # calls: the entry point allocates nothing, here or inside the library.
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    got = [ops.pack_static(r[0], r[1], r[2], sort=False) for r in results]
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.cuda.memory_reserved() == reserved_before
+    got = [_outputs(pk, r[3]) for pk, r in zip(got, results)]
+    for (packer, tok_d, a_len, T), g in zip(results, got):
+        ref = _outputs(packer.pack(tok_d, a_len, sort=False), T)
+        for k in ref:
+            assert np.array_equal(ref[k], g[k]), k
+
+
+def test_pack_static_empty_batch():
+    """T = 0: no segments, no tiles, and every count written (the counts array held other
+    values before the call)."""
+    from valora_b200 import ops
+    packer = ops.Packer(16, 4, DEV)
+    packer.counts.fill_(77)
+    tok = torch.zeros(0, dtype=torch.int64, device=DEV)
+    a_len = torch.full((4,), 64, dtype=torch.int64, device=DEV)
+    pk = ops.pack_static(packer, tok, a_len)
+    assert pk.counts.cpu().tolist() == [0] * 8
+    packer.counts.fill_(77)
+    assert packer.pack(tok, a_len).counts.cpu().tolist() == [0] * 8
 
 
 def test_pack_static_refuses_batches_beyond_its_scratch():

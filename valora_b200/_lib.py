@@ -19,7 +19,7 @@ _SIGS = {
     "vlr_version": (c_int, []),
     "vlr_error_string": (ctypes.c_char_p, [c_int]),
     "vlr_set_device": (c_int, [c_int]),
-    "vlr_debug_set_trace": (c_int, [c_vp, c_i64]),
+    "vlr_selftest_bounded_wait": (c_int, [c_i64, c_vp, c_vp, c_vp]),
     "vlr_device_status": (c_int, [c_int]),
     "vlr_bgmv": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp,
                          c_i64, c_i64, c_i64, c_int, c_int, c_vp]),
@@ -35,7 +35,7 @@ _SIGS = {
     "vlr_step_plan_bytes": (c_sz, [c_int]),
     "vlr_step_plan_build": (c_int, [c_vp, c_int, c_i64, c_int, c_vp]),
     "vlr_lora_step": (c_int, [c_vp, c_int, c_i64, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp,
-                              c_int, c_int, c_int, c_int, c_int, c_vp, c_sz, c_vp]),
+                              c_int, c_int, c_int, c_int, c_int, c_vp, c_sz, c_vp, c_vp]),
     "vlr_lora_step_workspace_bytes": (c_sz, [c_i64, c_int]),
 }
 
@@ -53,11 +53,12 @@ def load(build_if_missing: bool = True):
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB
+    trace = os.environ.get("VLR_TRACE") == "1"           # debugging build with the stage trace
+    path = _build.LIB_TRACE if trace else _build.LIB
     if not os.path.exists(path):
         if not build_if_missing:
             raise RuntimeError(f"{path} is missing: build it with `python -m valora_b200.build`")
-        _build.build()
+        _build.build(trace=trace)
     lib = ctypes.CDLL(path)
     for name in declared_symbols():
         if not hasattr(lib, name):
@@ -65,6 +66,8 @@ def load(build_if_missing: bool = True):
         if name in _SIGS:
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = _SIGS[name]
+    if hasattr(lib, "vlr_debug_set_trace"):          # debug builds (-DVLR_TRACE) only
+        lib.vlr_debug_set_trace.restype, lib.vlr_debug_set_trace.argtypes = c_int, [c_vp, c_i64]
     _lib = lib
     return lib
 

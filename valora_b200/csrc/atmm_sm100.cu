@@ -96,6 +96,15 @@ __device__ __forceinline__ void load_w_rows(uint32_t dst, const MapSet* ms, int 
   }
 }
 
+// Device-side status: bit 0 (1) a bounded wait gave up and the kernel returned early, bit 1
+// (2) a tile record was outside what the launch supports (rank above the launch's bound or not
+// a multiple of 8, more rows than a tile holds) and was skipped.  A step may name its own
+// status word (TileSource::status); the other entry points use this process-wide one.
+__device__ int g_status;
+__device__ __forceinline__ void raise_status(const TileSource& src, int bits) {
+  atomicOr(src.status != nullptr ? src.status : &g_status, bits);
+}
+
 // Item -> tile.  Warp-collective: all 32 lanes call it and all get the result.
 // mode 1: item = (problem * n_tiles + tile) * nsplit + split, n_tiles on the device.
 // mode 0: item = tile * nsplit + split over the reference's problem table; tiles
@@ -154,7 +163,8 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
   if (ti.valid) {
     if (ti.rank <= 0 || ti.rank > src.max_rank || (ti.rank & 7) || ti.rows <= 0 ||
         ti.rows > (ti.gather ? kGatherRows : kTileM)) {
-      ti.valid = 0;                  // host validated what it could; skip bad entries
+      ti.valid = 0;                  // host validated what it could; skip bad entries, and say so
+      if (lane == 0) raise_status(src, 2);
     } else {
       const int64_t* a_start = src.a_start;
       const int64_t* a_loc = src.a_loc;
@@ -277,12 +287,15 @@ __device__ __forceinline__ void feed_tiles(const TileSource& src, const ItemFeed
   }
 }
 
-__device__ int g_status;             // 0 ok, 1 a bounded wait gave up
-
-// Debug aid: CTA 0 stamps clock64 into src.trace, slot `what` of stage `k`.
+// Debug aid, compiled in with -DVLR_TRACE only: CTA 0 stamps clock64 into src.trace, slot
+// `what` of stage `k`.
 __device__ __forceinline__ void trace_stamp(const TileSource& src, uint32_t k, int what) {
+#ifdef VLR_TRACE
   if (src.trace != nullptr && blockIdx.x == 0 && (int64_t)k * 8 + what < src.trace_cap)
     src.trace[(int64_t)k * 8 + what] = clock64();
+#else
+  (void)src; (void)k; (void)what;
+#endif
 }
 
 // ============================================================================
@@ -564,7 +577,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
-  if (threadIdx.x == 0 && abort_s) g_status = 1;
+  if (threadIdx.x == 0 && abort_s) raise_status(src, 1);
 }
 
 // ============================================================================
@@ -1025,7 +1038,24 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
-  if (threadIdx.x == 0 && abort_s) g_status = 1;
+  if (threadIdx.x == 0 && abort_s) raise_status(src, 1);
+}
+
+// One CTA, one thread: wait on an mbarrier that nothing ever arrives on, with a budget of
+// `budget_cycles`, and report the give-up like the kernels above do.  Exercises the bounded
+// wait and the status path without any kernel having to go wrong.
+__global__ void bounded_wait_selftest_kernel(long long budget_cycles, int* status, long long* waited) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ volatile int abort_s;
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+    const long long t0 = clock64();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_s, budget_cycles);
+    if (waited != nullptr) *waited = clock64() - t0;
+    if (!ok && abort_s) atomicOr(status != nullptr ? status : &g_status, 1);
+  }
 }
 
 // ============================================================================
@@ -1084,8 +1114,10 @@ static int expand_splits(int64_t tiles, int h_out) {
   return (int)want;
 }
 
+#ifdef VLR_TRACE
 static long long* g_trace_ptr = nullptr;
 static int64_t g_trace_cap = 0;
+#endif
 
 static void size_rings(TileSource& src, int max_rank) {
   if (max_rank <= 0 || max_rank > kMaxRank) max_rank = kMaxRank;
@@ -1135,8 +1167,10 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
   // memory, h_in / h_out are maxima over its problems and only size the grid.
   MapSet maps;
   memset(&maps, 0, sizeof(maps));
+#ifdef VLR_TRACE
   src.trace = g_trace_ptr;
   src.trace_cap = g_trace_cap;
+#endif
   const bool step = src.plan != nullptr;
   // rank bound: the caller's hint in a step, the width of the rank-side buffer otherwise
   size_rings(src, step ? src.max_rank : (h_in >= h_out ? h_out : h_in));
@@ -1244,12 +1278,22 @@ extern "C" int vlr_device_status(int reset) {
   return v | d;
 }
 
-// Debug aid: while a device buffer is set, CTA 0 of the tensor-core kernels writes
-// clock64 stamps into it (8 int64 per pipeline stage: stage issued, operands seen
-// by the MMA thread, MMAs issued / epilogue started, stage released).
+extern "C" int vlr_selftest_bounded_wait(int64_t budget_cycles, int32_t* dev_status,
+                                         int64_t* dev_waited_cycles, void* stream) {
+  if (budget_cycles <= 0 || budget_cycles > 2000000000LL) return VLR_ERR_RANGE;
+  vlr::bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(
+      (long long)budget_cycles, dev_status, reinterpret_cast<long long*>(dev_waited_cycles));
+  return vlr::launch_status();
+}
+
+#ifdef VLR_TRACE
+// Debug builds (-DVLR_TRACE) only: while a device buffer is set, CTA 0 of the tensor-core
+// kernels writes clock64 stamps into it (8 int64 per pipeline stage: stage issued, operands
+// seen by the MMA thread, MMAs issued / epilogue started, stage released).
 extern "C" int vlr_debug_set_trace(void* dev_buffer, int64_t n_int64) {
   vlr::g_trace_ptr = reinterpret_cast<long long*>(dev_buffer);
   vlr::g_trace_cap = dev_buffer ? n_int64 : 0;
   vlr::bgmv_decode_set_trace(vlr::g_trace_ptr, vlr::g_trace_cap);
   return VLR_OK;
 }
+#endif

@@ -35,7 +35,11 @@ __device__ int g_decode_status;                // 1: a bounded wait gave up
 __device__ long long* g_decode_trace;
 __device__ long long g_decode_trace_cap;
 __device__ __forceinline__ void dec_stamp(long long slot) {
+#ifdef VLR_TRACE
   if (g_decode_trace != nullptr && blockIdx.x == 0 && slot < g_decode_trace_cap) g_decode_trace[slot] = clock64();
+#else
+  (void)slot;
+#endif
 }
 
 // Groups of one window, in shared memory for the whole CTA.

@@ -2,7 +2,7 @@
 // segments, exclusive-scan offsets and the tile schedule.  Integer work only;
 // every output is a pure function of the inputs (no atomics decide an order).
 //
-// Four small launches on one stream:
+// Four small launches on one stream (nothing has to be cleared ahead of them):
 //   1. pack_hist     per-block adapter histograms (blocks of kPackBlock tokens)
 //   2. pack_scan     per-adapter exclusive prefix over blocks + adapter bases
 //   3. pack_scatter  stable placement: perm and the sorted key array
@@ -55,22 +55,18 @@ static size_t pack_ws_layout(int64_t T, int64_t n_adapters, PackWs* ws, char* ba
   return off;
 }
 
-__device__ __forceinline__ int clamp_id(int64_t id, int n_adapters, int32_t* counts) {
-  if (id < 0 || id >= n_adapters) {
-    counts[VLR_COUNT_STATUS] = 1;
-    return 0;
-  }
-  return (int)id;
+// Ids outside [0, n_adapters) are served as adapter 0; pack_tiles reports them in the status.
+__device__ __forceinline__ int clamp_id(int64_t id, int n_adapters) {
+  return (id < 0 || id >= n_adapters) ? 0 : (int)id;
 }
 
 __global__ void __launch_bounds__(kPackBlock)
-pack_hist_kernel(const int64_t* __restrict__ tok, int T, int n_adapters, int32_t* hist,
-                 int32_t* counts) {
+pack_hist_kernel(const int64_t* __restrict__ tok, int T, int n_adapters, int32_t* hist) {
   extern __shared__ int32_t sh[];
   for (int a = threadIdx.x; a < n_adapters; a += kPackBlock) sh[a] = 0;
   __syncthreads();
   const int i = blockIdx.x * kPackBlock + threadIdx.x;
-  if (i < T) atomicAdd(&sh[clamp_id(tok[i], n_adapters, counts)], 1);
+  if (i < T) atomicAdd(&sh[clamp_id(tok[i], n_adapters)], 1);
   __syncthreads();
   int32_t* row = hist + (int64_t)blockIdx.x * n_adapters;
   for (int a = threadIdx.x; a < n_adapters; a += kPackBlock) row[a] = sh[a];
@@ -136,10 +132,10 @@ pack_scan_kernel(int nblk, int n_adapters, int32_t* hist, int32_t* abase) {
 __global__ void __launch_bounds__(kPackBlock)
 pack_scatter_kernel(const int64_t* __restrict__ tok, int T, int n_adapters,
                     const int32_t* __restrict__ hist, const int32_t* __restrict__ abase,
-                    int32_t* perm, int32_t* key, int32_t* counts) {
+                    int32_t* perm, int32_t* key) {
   __shared__ int keys[kPackBlock];
   const int i = blockIdx.x * kPackBlock + threadIdx.x;
-  const int k = i < T ? clamp_id(tok[i], n_adapters, counts) : -1;
+  const int k = i < T ? clamp_id(tok[i], n_adapters) : -1;
   keys[threadIdx.x] = k;
   __syncthreads();
   if (i >= T) return;
@@ -172,13 +168,18 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
   __shared__ int s_P, s_C;
   const int tid = threadIdx.x;
 
-  if (!sorted) {
-    for (int i = tid; i < T; i += kScanThreads) {
+  // every count is written by this kernel (nothing has to be cleared ahead of it); the
+  // status starts from the ids themselves
+  int bad = 0;
+  for (int i = tid; i < T; i += kScanThreads) {
+    const int64_t id = tok[i];
+    bad |= (id < 0 || id >= n_adapters) ? 1 : 0;
+    if (!sorted) {
       out.perm[i] = i;
-      ws.key[i] = clamp_id(tok[i], n_adapters, out.counts);
+      ws.key[i] = clamp_id(id, n_adapters);
     }
-    __syncthreads();
   }
+  bad = __syncthreads_or(bad);
   const int32_t* key = ws.key;
   const int32_t* row = out.perm;
 
@@ -296,12 +297,43 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     out.counts[VLR_COUNT_MMA_TILES] = n_mma;
     out.counts[VLR_COUNT_GATHER_TILES] = n_gather;
     out.counts[VLR_COUNT_GATHER_ROWS] = n_short;
-    if ((int64_t)n_mma + n_gather > out.tiles_cap) out.counts[VLR_COUNT_STATUS] = 2;
+    out.counts[VLR_COUNT_STATUS] = ((int64_t)n_mma + n_gather > out.tiles_cap) ? 2 : (bad ? 1 : 0);
+    for (int i = VLR_COUNT_STATUS + 1; i < VLR_COUNT_INTS; ++i) out.counts[i] = 0;
   }
 }
 
-__global__ void pack_clear_counts(int32_t* counts) {
-  if (threadIdx.x < VLR_COUNT_INTS) counts[threadIdx.x] = 0;
+// The packer's launches on scratch `ws` (caller workspace or the built-in array).
+static int pack_launch(const int64_t* tok_adapter, int64_t T, const int64_t* a_len, int64_t n_adapters,
+                       int sort, int tile_m, int mma_min_rows, int gather_rows_per_tile,
+                       const PackWs& ws, const PackOut& out, cudaStream_t s) {
+  const int nblk = (int)((T + kPackBlock - 1) / kPackBlock);
+  if (sort && T > 0) {
+    pack_hist_kernel<<<nblk, kPackBlock, n_adapters * sizeof(int32_t), s>>>(
+        tok_adapter, (int)T, (int)n_adapters, ws.hist);
+    pack_scan_kernel<<<1, kScanThreads, 0, s>>>(nblk, (int)n_adapters, ws.hist, ws.abase);
+    pack_scatter_kernel<<<nblk, kPackBlock, 0, s>>>(tok_adapter, (int)T, (int)n_adapters, ws.hist,
+                                                    ws.abase, out.perm, ws.key);
+  }
+  pack_tiles_kernel<<<1, kScanThreads, 0, s>>>(tok_adapter, a_len, (int)T, (int)n_adapters,
+                                               sort && T > 0, tile_m, mma_min_rows,
+                                               gather_rows_per_tile, ws, out);
+  return launch_status();
+}
+
+// Argument checks shared by the two packer entry points.
+static int pack_check(const int64_t* tok_adapter, int64_t T, const int64_t* a_len, int64_t n_adapters,
+                      int tile_m, int mma_min_rows, int gather_rows_per_tile, const PackOut& o) {
+  if (!a_len || !o.perm || !o.seg_len || !o.seg_rank || !o.seg_adapter || !o.seg_start || !o.tiles ||
+      !o.gather_rows || !o.counts)
+    return VLR_ERR_NULL;
+  if (T > 0 && !tok_adapter) return VLR_ERR_NULL;
+  if (T < 0 || T > (1 << 24) || n_adapters <= 0 || n_adapters > kPackMaxAdapters || o.tiles_cap < 0)
+    return VLR_ERR_RANGE;
+  // a tile is at most one 128-row MMA tile, or 16 gathered rows
+  if (tile_m <= 0 || tile_m > 128 || mma_min_rows <= 0 || gather_rows_per_tile <= 0 ||
+      gather_rows_per_tile > 16)
+    return VLR_ERR_RANGE;
+  return VLR_OK;
 }
 
 __global__ void var_len_copy_kernel(const int64_t* __restrict__ old_start,
@@ -328,33 +360,17 @@ extern "C" int vlr_pack(const int64_t* tok_adapter, int64_t T, const int64_t* a_
                         int32_t* tiles, int64_t tiles_cap, int32_t* gather_rows, int32_t* counts,
                         void* workspace, size_t workspace_bytes, void* stream) {
   using namespace vlr;
-  if (!a_len || !perm || !seg_len || !seg_rank || !seg_adapter || !seg_start || !tiles ||
-      !gather_rows || !counts || !workspace)
-    return VLR_ERR_NULL;
-  if (T > 0 && !tok_adapter) return VLR_ERR_NULL;
-  if (T < 0 || T > (1 << 24) || n_adapters <= 0 || n_adapters > kPackMaxAdapters || tiles_cap < 0)
-    return VLR_ERR_RANGE;
-  if (tile_m <= 0 || mma_min_rows <= 0 || gather_rows_per_tile <= 0) return VLR_ERR_RANGE;
+  PackOut out{perm, seg_len, seg_rank, seg_adapter, seg_start, tiles, tiles_cap, gather_rows, counts};
+  int rc = pack_check(tok_adapter, T, a_len, n_adapters, tile_m, mma_min_rows, gather_rows_per_tile, out);
+  if (rc != VLR_OK) return rc;
+  if (!workspace) return VLR_ERR_NULL;
   char* base = reinterpret_cast<char*>(align_up(reinterpret_cast<uintptr_t>(workspace), 256));
   const size_t slack = base - reinterpret_cast<char*>(workspace);
   PackWs ws;
   const size_t need = pack_ws_layout(T, n_adapters, &ws, base);
   if (need + slack > workspace_bytes) return VLR_ERR_WORKSPACE;
-  cudaStream_t s = (cudaStream_t)stream;
-  const int nblk = (int)((T + kPackBlock - 1) / kPackBlock);
-  pack_clear_counts<<<1, 32, 0, s>>>(counts);
-  if (sort && T > 0) {
-    pack_hist_kernel<<<nblk, kPackBlock, n_adapters * sizeof(int32_t), s>>>(
-        tok_adapter, (int)T, (int)n_adapters, ws.hist, counts);
-    pack_scan_kernel<<<1, kScanThreads, 0, s>>>(nblk, (int)n_adapters, ws.hist, ws.abase);
-    pack_scatter_kernel<<<nblk, kPackBlock, 0, s>>>(tok_adapter, (int)T, (int)n_adapters, ws.hist,
-                                                    ws.abase, perm, ws.key, counts);
-  }
-  PackOut out{perm, seg_len, seg_rank, seg_adapter, seg_start, tiles, tiles_cap, gather_rows, counts};
-  pack_tiles_kernel<<<1, kScanThreads, 0, s>>>(tok_adapter, a_len, (int)T, (int)n_adapters,
-                                               sort && T > 0, tile_m, mma_min_rows,
-                                               gather_rows_per_tile, ws, out);
-  return launch_status();
+  return pack_launch(tok_adapter, T, a_len, n_adapters, sort, tile_m, mma_min_rows,
+                     gather_rows_per_tile, ws, out, (cudaStream_t)stream);
 }
 
 extern "C" int vlr_var_len_copy(const int64_t* old_start, const int64_t* len,
@@ -430,32 +446,16 @@ extern "C" int vlr_pack_static(const int64_t* tok_adapter, int64_t T, const int6
                                int32_t* tiles, int64_t tiles_cap, int32_t* gather_rows,
                                int32_t* counts, void* stream) {
   using namespace vlr;
-  if (!a_len || !perm || !seg_len || !seg_rank || !seg_adapter || !seg_start || !tiles ||
-      !gather_rows || !counts)
-    return VLR_ERR_NULL;
-  if (T > 0 && !tok_adapter) return VLR_ERR_NULL;
-  if (T < 0 || n_adapters <= 0 || tiles_cap < 0) return VLR_ERR_RANGE;
-  if (tile_m <= 0 || mma_min_rows <= 0 || gather_rows_per_tile <= 0) return VLR_ERR_RANGE;
+  PackOut out{perm, seg_len, seg_rank, seg_adapter, seg_start, tiles, tiles_cap, gather_rows, counts};
+  int rc = pack_check(tok_adapter, T, a_len, n_adapters, tile_m, mma_min_rows, gather_rows_per_tile, out);
+  if (rc != VLR_OK) return rc;
   if (T > kStaticMaxTokens || n_adapters > kStaticMaxAdapters) return VLR_ERR_STATIC_LIMIT;
   unsigned char* scratch = nullptr;
-  int rc = static_scratch(&scratch);
+  rc = static_scratch(&scratch);
   if (rc != VLR_OK) return rc;
   PackWs ws;
   const size_t need = pack_ws_layout(T, n_adapters, &ws, reinterpret_cast<char*>(scratch));
   if (need > kStaticScratchBytes) return VLR_ERR_STATIC_LIMIT;
-  cudaStream_t s = (cudaStream_t)stream;
-  const int nblk = (int)((T + kPackBlock - 1) / kPackBlock);
-  pack_clear_counts<<<1, 32, 0, s>>>(counts);
-  if (sort && T > 0) {
-    pack_hist_kernel<<<nblk, kPackBlock, n_adapters * sizeof(int32_t), s>>>(
-        tok_adapter, (int)T, (int)n_adapters, ws.hist, counts);
-    pack_scan_kernel<<<1, kScanThreads, 0, s>>>(nblk, (int)n_adapters, ws.hist, ws.abase);
-    pack_scatter_kernel<<<nblk, kPackBlock, 0, s>>>(tok_adapter, (int)T, (int)n_adapters, ws.hist,
-                                                    ws.abase, perm, ws.key, counts);
-  }
-  PackOut out{perm, seg_len, seg_rank, seg_adapter, seg_start, tiles, tiles_cap, gather_rows, counts};
-  pack_tiles_kernel<<<1, kScanThreads, 0, s>>>(tok_adapter, a_len, (int)T, (int)n_adapters,
-                                               sort && T > 0, tile_m, mma_min_rows,
-                                               gather_rows_per_tile, ws, out);
-  return launch_status();
+  return pack_launch(tok_adapter, T, a_len, n_adapters, sort, tile_m, mma_min_rows,
+                     gather_rows_per_tile, ws, out, (cudaStream_t)stream);
 }

@@ -84,9 +84,11 @@ struct TileSource {
   const StepProblem* plan;
   void* vbuf;
   int64_t vstride;
-  // optional timing trace of CTA 0 (clock64 stamps, 4 per pipeline stage); null = off
+  // debug builds: timing trace of CTA 0 (clock64 stamps, 8 per pipeline stage); null = off
   long long* trace;
   int64_t trace_cap;
+  // device status word of this launch (see raise_status); null = the process-wide one
+  int* status;
   // work distribution: null = item k of a CTA is blockIdx.x + k * gridDim.x; else a
   // zeroed device counter from which the CTAs draw their next item (after the first)
   unsigned int* item_counter;

@@ -56,7 +56,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  abort_flag lives in shared memory; any role that gives up sets
 // it and every other role sees it within a few hundred polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long budget = kWaitCycleBudget) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t it = 0;
@@ -64,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++it & 255u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycleBudget) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1;
         return false;
       }

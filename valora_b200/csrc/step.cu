@@ -52,7 +52,7 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
                              const int32_t* gather_rows, int64_t max_mma_tiles,
                              int64_t max_gather_tiles, const int32_t* counts, const void* scales,
                              int max_h_in, int max_h_out, int max_rank, int dtype, int phase_mask,
-                             void* workspace, size_t workspace_bytes, void* stream) {
+                             void* workspace, size_t workspace_bytes, int32_t* dev_status, void* stream) {
   if (T == 0 || n_problems == 0) return VLR_OK;
   if (!plan_dev || !tiles || !gather_rows || !counts || !scales || !workspace) return VLR_ERR_NULL;
   if (dtype != VLR_F16 && dtype != VLR_BF16) return VLR_ERR_DTYPE;
@@ -78,6 +78,7 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   src.vbuf = vb;
   src.vstride = T * kMaxRank;
   src.gather_rows = gather_rows;
+  src.status = dev_status;
   src.max_rank = (max_rank > 0 && max_rank <= kMaxRank) ? max_rank : kMaxRank;
   src.gather_mma = (phase_mask & VLR_STEP_GATHER_ON_TENSOR_CORES) ? 1 : 0;
   src.wide_gather = (phase_mask & VLR_STEP_WIDE_GATHER_STAGES) ? 1 : 0;

@@ -28,7 +28,8 @@ class LoraStepEngine:
                  scalings: Sequence[float], dtype, device, layers: int, max_tokens: int,
                  tile_m: int = 128, mma_min_rows: int = 16, gather_rows_per_tile: Optional[int] = None,
                  alloc_activations: bool = True, gather_path: str = "mma",
-                 wide_gather: Optional[bool] = None, input_of: Optional[Sequence[int]] = None):
+                 wide_gather: Optional[bool] = None, input_of: Optional[Sequence[int]] = None,
+                 share_pools_with: Optional["LoraStepEngine"] = None):
         """input_of[p] = the projection whose activations projection p reads (itself by
         default).  q, k and v of a transformer layer read the same rows, as do gate and
         up (lora_unordered_batch_infer.py:946-965 passes one `input_embs` view to three
@@ -39,7 +40,10 @@ class LoraStepEngine:
         tokens) through the tensor-core kernels with gathered rows (up to 128 rows of
         an adapter per tile); "simt" sends them through the gather mat-vec kernels
         (8 rows per tile).  wide_gather: let a gather stage of the expand take as many
-        columns as fit (default: when an adapter of rank 32 or less is resident)."""
+        columns as fit (default: when an adapter of rank 32 or less is resident).
+        share_pools_with: another engine over the same projections and adapters whose
+        adapter pools this one uses instead of allocating its own (a second view of the
+        same resident weights, e.g. with other activation buffers)."""
         if gather_path not in ("mma", "simt"):
             raise ValueError("gather_path must be 'mma' or 'simt'")
         self.gather_path = gather_path
@@ -74,13 +78,19 @@ class LoraStepEngine:
             self.slot_b[p] = (ho, nb.get(ho, 0))
             nb[ho] = nb.get(ho, 0) + 1
         tot_rank = sum(self.ranks)
-        self.pool_a = {w: AdapterPool(tot_rank * n + 16, w, n, dtype, self.device, self.layers) for w, n in na.items()}
-        self.pool_b = {w: AdapterPool(tot_rank * n + 16, w, n, dtype, self.device, self.layers) for w, n in nb.items()}
-        for a in range(n_ad):
-            for pools in (self.pool_a, self.pool_b):
-                for pool in pools.values():
-                    pool.load_adapter(f"adapter{a}", self.ranks[a], float(scalings[a]),
-                                      [[None] * pool.n_slots for _ in range(self.layers)])
+        if share_pools_with is not None:
+            other = share_pools_with
+            if other.projections != self.projections or other.ranks != self.ranks or other.layers != self.layers:
+                raise ValueError("pools can be shared only between engines over the same projections, adapters and layers")
+            self.pool_a, self.pool_b = other.pool_a, other.pool_b
+        else:
+            self.pool_a = {w: AdapterPool(tot_rank * n + 16, w, n, dtype, self.device, self.layers) for w, n in na.items()}
+            self.pool_b = {w: AdapterPool(tot_rank * n + 16, w, n, dtype, self.device, self.layers) for w, n in nb.items()}
+            for a in range(n_ad):
+                for pools in (self.pool_a, self.pool_b):
+                    for pool in pools.values():
+                        pool.load_adapter(f"adapter{a}", self.ranks[a], float(scalings[a]),
+                                          [[None] * pool.n_slots for _ in range(self.layers)])
         any_pool = next(iter(self.pool_a.values()))
         self.a_len = any_pool.a_len
         self.scales = any_pool.a_scaling
@@ -121,6 +131,7 @@ class LoraStepEngine:
                 for layer in range(self.layers):
                     buf = pool.buffer[layer]
                     buf.copy_((torch.randn(buf.shape, generator=g, device=self.device, dtype=torch.float32) * std).to(self.dtype))
+                pool._pristine[:] = False            # free cells no longer read as zeros
 
     def adapter_weights(self, layer: int, proj: int, adapter: int):
         """(A [h_in, r], B [r, h_out]) read back from the pools."""

@@ -5,7 +5,8 @@
     python -m valora_b200.microbench --config 1 --api step   # the same decode batch through the step API
     python -m valora_b200.microbench --config 2     # prefill, mixed ranks 8..128, fp16, 7 projections (step API)
     python -m valora_b200.microbench --config 3 --shared-x   # the mixed batch with q/k/v and up/gate reading one X each
-    python -m valora_b200.microbench --config 3 --trace expand   # stage timing of one launch (clock64 stamps of CTA 0)
+    VLR_TRACE=1 python -m valora_b200.microbench --config 3 --trace expand   # stage timing of one launch (clock64 stamps
+                                                     # of CTA 0; needs the debugging build: python -m valora_b200.build --trace)
     python -m valora_b200.microbench --config 4     # 16384 tokens, 1024 adapters, ranks 16..128, bf16 (step API)
 
 Configs 0 and 1:  A measurement walks `--layers` independent copies
@@ -278,6 +279,9 @@ def trace_step(config: int, layers: int, phase: str, dev):
     from . import _lib
     from .engine import LoraStepEngine
     lib = _lib.load()
+    if not hasattr(lib, "vlr_debug_set_trace"):
+        raise SystemExit("the stage trace is compiled into debugging builds only: "
+                         "python -m valora_b200.build --trace, then run with VLR_TRACE=1")
     b = workloads.CONFIGS[config]()
     b.layers = layers
     eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T)

@@ -4,7 +4,9 @@ stream.  There is no CPU or eager fallback: a missing library or a non-CUDA
 tensor raises."""
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -20,6 +22,23 @@ MAX_RANK = 128
 PHASE_SHRINK_MMA, PHASE_SHRINK_GATHER, PHASE_EXPAND_MMA, PHASE_EXPAND_GATHER, PHASE_ALL = 1, 2, 4, 8, 15
 STEP_GATHER_ON_TENSOR_CORES = 16
 STEP_WIDE_GATHER_STAGES = 32
+
+
+_NVTX = os.environ.get("VLR_NVTX") == "1"
+
+
+@contextlib.contextmanager
+def _nvtx(name: str):
+    """NVTX range around an operator call when VLR_NVTX=1 (for timeline profilers); the
+    reference has no ranges of its own around these calls."""
+    if not _NVTX:
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -95,9 +114,10 @@ def bgmv(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies, qkvo, lora
         if lora_scales.dtype != x.dtype:
             raise RuntimeError("lora_scales must have the dtype of x")
     lib = _bind(x.device)
-    rc = lib.vlr_bgmv(_ptr(y), _ptr(x), _ptr(w), _ptr(start_indicies), _ptr(lora_ranks),
-                      _ptr(loc_indicies), _ptr(indicies), int(qkvo), _ptr(lora_scales),
-                      x.size(0), h_in, h_out, _dtype_code(x), int(layout), _stream(x.device))
+    with _nvtx("vlr.bgmv_shrink" if h_in >= h_out else "vlr.bgmv_expand"):
+        rc = lib.vlr_bgmv(_ptr(y), _ptr(x), _ptr(w), _ptr(start_indicies), _ptr(lora_ranks),
+                          _ptr(loc_indicies), _ptr(indicies), int(qkvo), _ptr(lora_scales),
+                          x.size(0), h_in, h_out, _dtype_code(x), int(layout), _stream(x.device))
     if rc in (-2,):
         raise RuntimeError(f"No suitable kernel. h_in={h_in} h_out={h_out} dtype={x.dtype}")
     _lib.check(rc, "vlr_bgmv")
@@ -131,12 +151,13 @@ def atmm(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies, qkvo, lora
     if apply_scale:
         _check_input(lora_scales, "lora_scales")
     lib = _bind(x.device)
-    rc = lib.vlr_atmm(_ptr(y), _ptr(x), _ptr(w), _ptr(start_indicies), _ptr(lora_ranks),
-                      _ptr(loc_indicies), _ptr(indicies), int(qkvo), _ptr(lora_scales),
-                      _ptr(output_counts), _ptr(rank_counts), _ptr(lora_ids), _ptr(start_ids),
-                      _ptr(tmp_d), 0 if tmp_d is None else tmp_d.numel() * tmp_d.element_size(),
-                      num_problems, x.size(0), h_in, h_out, w.size(0), _dtype_code(x), flags,
-                      _stream(x.device))
+    with _nvtx("vlr.atmm_shrink" if h_in >= h_out else "vlr.atmm_expand"):
+        rc = lib.vlr_atmm(_ptr(y), _ptr(x), _ptr(w), _ptr(start_indicies), _ptr(lora_ranks),
+                          _ptr(loc_indicies), _ptr(indicies), int(qkvo), _ptr(lora_scales),
+                          _ptr(output_counts), _ptr(rank_counts), _ptr(lora_ids), _ptr(start_ids),
+                          _ptr(tmp_d), 0 if tmp_d is None else tmp_d.numel() * tmp_d.element_size(),
+                          num_problems, x.size(0), h_in, h_out, w.size(0), _dtype_code(x), flags,
+                          _stream(x.device))
     if rc in (-2,):
         raise RuntimeError(f"No suitable kernel. h_in={h_in} h_out={h_out} dtype={x.dtype}")
     _lib.check(rc, "vlr_atmm")
@@ -167,6 +188,8 @@ class Packer:
 
     def __init__(self, max_tokens: int, n_adapters: int, device, tile_m: int = 128,
                  mma_min_rows: int = 16, gather_rows_per_tile: int = 8):
+        if not (0 < tile_m <= 128) or mma_min_rows <= 0 or not (0 < gather_rows_per_tile <= 16):
+            raise RuntimeError("a tile holds at most 128 consecutive rows or 16 gathered rows")
         self.lib = _bind(torch.device(device))
         self.device = torch.device(device)
         self.max_tokens, self.n_adapters = int(max_tokens), int(n_adapters)
@@ -192,15 +215,22 @@ class Packer:
         T = tok_adapter.numel()
         if T > self.max_tokens or a_len.numel() != self.n_adapters:
             raise RuntimeError("batch exceeds the packer's capacity")
-        rc = self.lib.vlr_pack(_ptr(tok_adapter), T, _ptr(a_len), self.n_adapters, int(bool(sort)),
+        if tok_adapter.device != self.device or a_len.device != self.device:
+            raise RuntimeError("the batch lives on another device than the packer's buffers")
+        _bind(self.device)
+        with _nvtx("vlr.pack"):
+            rc = self._pack(tok_adapter, a_len, T, sort)
+        _lib.check(rc, "vlr_pack")
+        return Packed(T, self.perm, self.seg_len, self.seg_rank, self.seg_adapter, self.seg_start,
+                      self.tiles, self.gather_rows, self.counts, self.workspace)
+
+    def _pack(self, tok_adapter, a_len, T, sort):
+        return self.lib.vlr_pack(_ptr(tok_adapter), T, _ptr(a_len), self.n_adapters, int(bool(sort)),
                                self.tile_m, self.mma_min_rows, self.grp, _ptr(self.perm),
                                _ptr(self.seg_len), _ptr(self.seg_rank), _ptr(self.seg_adapter),
                                _ptr(self.seg_start), _ptr(self.tiles), self.tiles.size(0),
                                _ptr(self.gather_rows), _ptr(self.counts), _ptr(self.workspace),
                                self.workspace.numel(), _stream(self.device))
-        _lib.check(rc, "vlr_pack")
-        return Packed(T, self.perm, self.seg_len, self.seg_rank, self.seg_adapter, self.seg_start,
-                      self.tiles, self.gather_rows, self.counts, self.workspace)
 
 
 def pack_static(packer: "Packer", tok_adapter: torch.Tensor, a_len: torch.Tensor,
@@ -218,6 +248,9 @@ def pack_static(packer: "Packer", tok_adapter: torch.Tensor, a_len: torch.Tensor
     T = tok_adapter.numel()
     if T > packer.max_tokens or a_len.numel() != packer.n_adapters:
         raise RuntimeError("batch exceeds the packer's output capacity")
+    if tok_adapter.device != packer.device or a_len.device != packer.device:
+        raise RuntimeError("the batch lives on another device than the packer's buffers")
+    _bind(packer.device)           # the built-in scratch is the current device's: make it the packer's
     rc = packer.lib.vlr_pack_static(_ptr(tok_adapter), T, _ptr(a_len), packer.n_adapters,
                                     int(bool(sort)), packer.tile_m, packer.mma_min_rows, packer.grp,
                                     _ptr(packer.perm), _ptr(packer.seg_len), _ptr(packer.seg_rank),
@@ -323,10 +356,12 @@ class StepPlan:
 
     def run(self, packed: Packed, scales: torch.Tensor, max_mma_tiles: int = 0,
             max_gather_tiles: int = 0, phase_mask: int = PHASE_ALL, max_rank: int = 0,
-            first: int = 0, count: Optional[int] = None):
+            first: int = 0, count: Optional[int] = None, status: Optional[torch.Tensor] = None):
         """Enqueue shrink + expand for the packed batch: of every problem, or of
         problems [first, first + count) (they share the front of the workspace, so
-        sub-ranges of one plan must run on one stream)."""
+        sub-ranges of one plan must run on one stream).  status: an int32 device
+        tensor of one element the kernels OR their status bits into (the caller
+        clears and reads it); default: the process-wide word behind device_status()."""
         count = self.n - first if count is None else int(count)
         if first < 0 or count < 1 or first + count > self.n:
             raise RuntimeError("problem range outside the plan")
@@ -335,16 +370,35 @@ class StepPlan:
             raise RuntimeError("scales must have the plan's dtype")
         if packed.T > self.max_rows:
             raise RuntimeError("batch has more rows than the plan's buffers")
+        if status is not None:
+            _check_input(status, "status")
+            if status.dtype != torch.int32 or status.numel() < 1:
+                raise RuntimeError("status must be an int32 tensor")
         ws = self.workspace(packed.T)
         plan_ptr = ctypes.c_void_p(self.plan.data_ptr() + first * (self.plan.numel() // self.n))
-        rc = self.lib.vlr_lora_step(plan_ptr, count, packed.T, _ptr(packed.tiles),
-                                    _ptr(packed.gather_rows), int(max_mma_tiles),
-                                    int(max_gather_tiles), _ptr(packed.counts), _ptr(scales),
-                                    self.max_h_in, self.max_h_out, int(max_rank),
-                                    F16 if self.dtype == torch.float16 else BF16, int(phase_mask), _ptr(ws),
-                                    ws.numel(), _stream(self.device))
+        _bind(self.device)
+        with _nvtx("vlr.lora_step"):
+            rc = self.lib.vlr_lora_step(plan_ptr, count, packed.T, _ptr(packed.tiles),
+                                        _ptr(packed.gather_rows), int(max_mma_tiles),
+                                        int(max_gather_tiles), _ptr(packed.counts), _ptr(scales),
+                                        self.max_h_in, self.max_h_out, int(max_rank),
+                                        F16 if self.dtype == torch.float16 else BF16, int(phase_mask), _ptr(ws),
+                                        ws.numel(), _ptr(status), _stream(self.device))
         _lib.check(rc, "vlr_lora_step")
 
 
 def device_status(reset: bool = True) -> int:
+    """The process-wide device status word (bit 1: a bounded wait gave up, bit 2: a tile
+    record was skipped); synchronises the device."""
     return _lib.load().vlr_device_status(int(reset))
+
+
+def selftest_bounded_wait(budget_cycles: int, device, status: Optional[torch.Tensor] = None) -> int:
+    """Run the wait that nothing completes (see vlr_selftest_bounded_wait); returns the
+    cycles it took to give up."""
+    device = torch.device(device)
+    lib = _bind(device)
+    waited = torch.zeros(1, dtype=torch.int64, device=device)
+    rc = lib.vlr_selftest_bounded_wait(int(budget_cycles), _ptr(status), _ptr(waited), _stream(device))
+    _lib.check(rc, "vlr_selftest_bounded_wait")
+    return int(waited.item())

@@ -28,6 +28,7 @@ class AdapterPool:
         # zero-filled so that rows padded up to a multiple of 16 read as zeros
         self.buffer = torch.zeros((self.layers, self.cells, self.width), dtype=dtype, device=self.device)
         self.mem_state = np.ones(self.cells, dtype=np.uint8)       # 1 = free
+        self._pristine = np.ones(self.cells, dtype=bool)           # cell never written: still reads as zeros
         self.names: List[str] = []
         self.idx_map: Dict[str, int] = {}
         self.ranks: List[int] = []
@@ -77,6 +78,11 @@ class AdapterPool:
         need = self.n_slots * rank
         loc = self.alloc_contiguous(need) if contiguous else self.alloc(need)
         if loc is None:
+            # enough cells are free but no run of them is long enough: close the holes
+            # that offloaded adapters left and try again
+            self.defragment()
+            loc = self.alloc_contiguous(need)
+        if loc is None:
             raise Exception(f"no contiguous run of {need} cells is free")
         loc_t = torch.from_numpy(loc).to(self.device)
         for layer in range(self.layers):
@@ -84,9 +90,14 @@ class AdapterPool:
                 blk = slots[layer][p]
                 cells = loc_t[p * rank:(p + 1) * rank]
                 if blk is None:
-                    continue                     # the pool starts zero-filled
+                    # a projection the adapter does not touch contributes nothing: zeros, as the
+                    # reference packs them (lora_layer_weight.py safe()).  Freed cells keep the
+                    # previous owner's weights, so the fill cannot be skipped.
+                    if not self._pristine[loc].all():
+                        self.buffer[layer].index_fill_(0, cells, 0)
                 else:
                     self.buffer[layer][cells] = blk.to(device=self.device, dtype=self.dtype).reshape(rank, self.width)
+        self._pristine[loc] = False
         idx = len(self.names)
         self.idx_map[name] = idx
         self.names.append(name)
@@ -126,6 +137,26 @@ class AdapterPool:
         self.names = [self.names[i] for i in keep]
         self.ranks = [self.ranks[i] for i in keep]
         self.idx_map = {n: i for i, n in enumerate(self.names)}
+
+    def defragment(self):
+        """Move the resident adapters' cells to the front of the pool, in table order, so
+        that the free cells form one run behind them.  Every slot stays a run of
+        consecutive cells (what the tensor-core kernels need, as reference ATMM does:
+        atmm/valora/csrc/bgmv/bgmv_impl.cuh:89-92); a_loc is rewritten, a_start / a_len
+        do not change.  Device-side copies on the current stream, one layer at a time."""
+        used = int(self.a_loc.numel())
+        if used == 0:
+            self.mem_state[:] = 1
+            return
+        new_loc = torch.arange(used, dtype=torch.int64, device=self.device)
+        if not torch.equal(new_loc, self.a_loc):
+            for layer in range(self.layers):
+                moved = self.buffer[layer].index_select(0, self.a_loc)     # a copy: sources may overlap targets
+                self.buffer[layer][:used] = moved
+            self.a_loc = new_loc
+        self.mem_state[:used] = 0
+        self.mem_state[used:] = 1
+        self._pristine[:] = False
 
     def __init_tables(self):
         self.names, self.idx_map, self.ranks = [], {}, []

@@ -198,9 +198,11 @@ def dispatch_rows(rows: torch.Tensor, tok_adapter: torch.Tensor, plan: ExchangeP
     unsharded batch; kernels always read local memory."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
-    send_counts = torch.from_numpy(plan.send_counts)
-    recv_counts = torch.empty(world, dtype=torch.int64)
+    # the counts travel on the rows' device: an NCCL group has no CPU backend, gloo has no CUDA one
+    send_counts = torch.from_numpy(plan.send_counts).to(rows.device)
+    recv_counts = torch.empty(world, dtype=torch.int64, device=rows.device)
     dist.all_to_all_single(recv_counts, send_counts, group=group)
+    send_counts, recv_counts = send_counts.cpu(), recv_counts.cpu()
     order = torch.from_numpy(plan.send_order).to(rows.device)
     send_rows = rows.index_select(0, order).contiguous()
     send_ids = tok_adapter.index_select(0, order).contiguous()
