@@ -50,6 +50,8 @@ LAYERS = 32
 CFG4_LAYERS = 8          # independent copies of config 4's projection walked per step (larger than L2 together)
 CFG4_TOPK = 16           # adapters replicated on every GPU in the second config-4 run
 TOL = 1e-2
+OWN_ALLOWANCE = 2e-3
+ACT_SEED = 7919          # activations are drawn from another stream than the weights
 
 
 def env_int(name, default):
@@ -169,11 +171,12 @@ def phase_bytes(batch, tiles, n_mma, n_gather, merged):
 
 # --------------------------------------------------------------------------- parity (the oracle as checker)
 def out_tolerance(ref32, dtype):
-    """1e-2, or half an ulp of the 16-bit output type where its grid is coarser than that."""
+    """1e-2; where the 16-bit output grid is too coarse for that (bf16, |y| >= 4): half an ulp
+    of the output type plus 2e-3 for the kernels' own error (16-bit shrink result)."""
     prec = 8 if dtype == torch.bfloat16 else 11
     mag = ref32.abs().clamp_min(1e-30)
     half_ulp = torch.exp2(torch.floor(torch.log2(mag)) - prec)
-    return torch.maximum(torch.full_like(ref32, TOL), half_ulp * 1.01 + 1e-4), half_ulp
+    return torch.maximum(torch.full_like(ref32, TOL), half_ulp + OWN_ALLOWANCE), half_ulp
 
 
 def parity_step(eng, tok_np, ranks, scalings, dtype, sample):
@@ -208,7 +211,7 @@ def parity_step(eng, tok_np, ranks, scalings, dtype, sample):
         worst_abs = max(worst_abs, float(err.max()))
     return {"checked_problems": len(sample), "problems": [list(lp) for lp in sample],
             "oracle": "ragged_lora_ref_fp32 (fp32 arithmetic on the 16-bit inputs)",
-            "bound": "1e-2, or half an ulp of bf16 where that is larger",
+            "bound": "1e-2, or half an ulp of bf16 + 2e-3 where that is larger (|y| >= 4)",
             "max_excess": worst, "max_abs_err": worst_abs, "max_err_beyond_half_ulp": worst_own,
             "packing_bit_exact": packing_ok, "ok": bool(worst <= 0.0 and packing_ok)}
 
@@ -330,7 +333,7 @@ def config4_block(dist, dev, rank, world, steps, warmup, peak):
             eng = LoraStepEngine([("q", H, H)], ranks, scal, torch.bfloat16, dev, CFG4_LAYERS, T)
             eng.randomize_weights(seed=4 + rank)
             gen = torch.Generator(device=dev)
-            gen.manual_seed(4 + rank)
+            gen.manual_seed(4 + rank + ACT_SEED)
             for l in range(CFG4_LAYERS):
                 eng.x[l][0].normal_(generator=gen)
                 eng.y[l][0].normal_(generator=gen)
@@ -421,7 +424,7 @@ def main():
                          args.layers, T, gather_path=args.gather_path)
     eng.randomize_weights(seed=batch.seed)
     g = torch.Generator(device=dev)
-    g.manual_seed(batch.seed)
+    g.manual_seed(batch.seed + ACT_SEED)
     for layer in range(args.layers):
         for p in range(len(batch.projections)):
             eng.x[layer][p].normal_(generator=g)

@@ -177,6 +177,33 @@ int vlr_pack_static(const int64_t* tok_adapter, int64_t T, const int64_t* a_len,
 int vlr_var_len_copy(const int64_t* old_start, const int64_t* len, const int64_t* old_loc,
                      const int64_t* new_start, int64_t* new_loc, int64_t n, void* stream);
 
+/*
+ * The tile table: what a launch of the tensor-core kernels is shaped like, per
+ * kind of call and rank bound.  Replaces the reference's table of six CUTLASS
+ * tile integers per (adapters, first sequence length, K, N), measured on an
+ * Ampere part (valora/models/peft/lora_unordered_batch_infer.py:25-172,216-236;
+ * search space atmm/valora/csrc/bgmv/bgmv_config.h:11-31).  Here the MMA tile
+ * is fixed by the instruction (128 rows); what is chosen is how the 192 KB
+ * operand ring is cut into stages - which sets how many K blocks (shrink) or
+ * 64-column blocks (expand) of a tile travel together, i.e. how long the
+ * contiguous piece of every row is that one stage requests - and the row count
+ * of the tiles of a drop-in shrink with few rows.  An entry applies to launches
+ * whose rank bound is <= max_rank (the entry with the smallest such max_rank
+ * wins).  The table is process-wide; set it before launching, not concurrently
+ * with launches.  valora_b200/tile_table.json holds the measured table and the
+ * autotuner that writes it is `python -m valora_b200.autotune`.
+ */
+typedef struct {
+  int32_t max_rank;        /* 8..128 */
+  int32_t step;            /* 1: launches of vlr_lora_step, 0: single vlr_atmm calls */
+  int32_t shrink_stages;   /* 2, 3 or 4 stages of 96 / 64 / 48 KB; ranks above 64 need <= 3 */
+  int32_t expand_stages;   /* 3 or 4 stages of 64 / 48 KB; ranks above 64 need 3 */
+  int32_t small_call_rows; /* vlr_atmm shrink with T/128 + num_problems <= half the SMs: 32, 64 or 128 */
+  int32_t reserved;        /* 0 */
+} vlr_tile_choice_t;
+int vlr_set_tile_table(const vlr_tile_choice_t* entries, int n);   /* n <= 16; n = 0: built-in rules */
+int vlr_get_tile_choice(int step, int max_rank, vlr_tile_choice_t* out);
+
 /* Bind the calling thread's CUDA runtime state to a device (cudaSetDevice). */
 int vlr_set_device(int device);
 

@@ -2,7 +2,8 @@
 same seeded inputs.  Bit-exact for packing and index tables.  Floating point:
 every output element is within 1e-2 of the oracle's fp32 result; where the
 output's own 16-bit grid is coarser than that (bf16 at |y| >= 4 has a half-ulp
-of 0.0156) the bound is the half-ulp of the output type at that magnitude."""
+of 0.0156) the bound is the half-ulp of the output type at that magnitude plus
+2e-3 for the kernels' own error, which the step tests also assert on its own."""
 import numpy as np
 import pytest
 import torch
@@ -15,8 +16,8 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-2
 # bound on the kernels' own error (accumulation order, the 16-bit shrink result between the
 # two kernels), i.e. on what is left of |got - fp32 truth| once half an ulp of the output
-# type is taken off: half of TOL
-OWN_TOL = 5e-3
+# type is taken off: a fifth of TOL
+OWN_TOL = 2e-3
 DEV = "cuda:0"
 
 

@@ -20,6 +20,8 @@ _SIGS = {
     "vlr_error_string": (ctypes.c_char_p, [c_int]),
     "vlr_set_device": (c_int, [c_int]),
     "vlr_selftest_bounded_wait": (c_int, [c_i64, c_vp, c_vp, c_vp]),
+    "vlr_set_tile_table": (c_int, [c_vp, c_int]),
+    "vlr_get_tile_choice": (c_int, [c_int, c_int, c_vp]),
     "vlr_device_status": (c_int, [c_int]),
     "vlr_bgmv": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_vp,
                          c_i64, c_i64, c_i64, c_int, c_int, c_vp]),
@@ -66,6 +68,8 @@ def load(build_if_missing: bool = True):
         if name in _SIGS:
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = _SIGS[name]
+    from . import tile_table
+    tile_table.apply(lib)                            # the measured launch choices, if a table is committed
     if hasattr(lib, "vlr_debug_set_trace"):          # debug builds (-DVLR_TRACE) only
         lib.vlr_debug_set_trace.restype, lib.vlr_debug_set_trace.argtypes = c_int, [c_vp, c_i64]
     _lib = lib

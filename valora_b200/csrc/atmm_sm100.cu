@@ -392,6 +392,10 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
     // lane 0: TMA boxes (weights; consecutive activation rows).  Gather tiles: lane i
     // fetches row i with a one-row box into row slot i; the copy engine applies the
     // 128-byte swizzle from the address bits, so the slots form a dense tile.
+    // A producer waits for the release of the stage it is about to refill by phase parity, so
+    // it must never get more than one round of the ring ahead of the release it waits for:
+    // no more producers than stages (with two stages warp 2 only follows the item sequence).
+    constexpr int nprod = NST < kShrinkProducers ? NST : kShrinkProducers;
     uint32_t kiter = 0;
     bool ok = true;
     for (uint32_t ik = 0; ok; ++ik) {
@@ -412,7 +416,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       const uint32_t blk_bytes =
           (uint32_t)((ti.gather ? ti.rows : act_rows_loaded(ti.rows)) + n_pad) * 128u;
       for (int st = 0; st < nstages; ++st, ++kiter) {
-        if ((int)(kiter % kShrinkProducers) != warp) continue;   // another producer's stage
+        if ((int)(kiter % nprod) != warp) continue;              // another producer's stage
         const int s = kiter % nst;
         const int kb0 = st * sl.kbs;
         const int nsub = min(sl.kbs, kblocks - kb0);
@@ -648,6 +652,8 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
   const uint32_t a_tile = base;
   constexpr int nst = NST;                             // 3 stages of 64 KB or 4 of 48 KB
   constexpr uint32_t stage_bytes = kRingBytes / NST;
+  constexpr int nacc = kExpAccBufs;                    // accumulators in tensor memory, 128 columns each
+  constexpr uint32_t acc_cols = 512 / nacc;
   auto b_stage = [&](int s) { return base + kExpABytes + (uint32_t)s * stage_bytes; };
   const uint32_t bars = base + kExpABytes + kRingBytes;
   auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -692,8 +698,8 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
     // ------------------------------------------------------------ producers (stage k -> warp k % 2)
     const int pw = warp - kExpProdWarp0;
     // lane 0: TMA boxes (B rows; consecutive Y rows).  Gather tiles: lane i copies the
-    // 128-byte pieces of Y row i with 1-D bulk copies, packed 16 rows x 128 bytes per
-    // 64-column block (read back by the epilogue only, so no swizzle).
+    // stage's columns of Y row i with one 1-D bulk copy, rows packed row-major (read back
+    // by the epilogue only, so no swizzle).
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t ik = 0; ok; ++ik) {
@@ -720,7 +726,7 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
           if (ok) {
             trace_stamp(src, it, 0);
             uint32_t bytes = (uint32_t)ncb * (uint32_t)(k_pad + y_rows) * 128u;
-            if (WIDE && ti.gather)
+            if (ti.gather)
               bytes = (uint32_t)ncb * (uint32_t)k_pad * 128u +
                       (uint32_t)y_rows * (uint32_t)min(er.tile_n, er.h_out - n0) * 2u;
             mbar_expect_tx(full_bar(s), bytes);
@@ -737,15 +743,10 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         if (ti.gather) {
           ok = __shfl_sync(0xffffffffu, ok, 0);        // also orders expect_tx before the copies
           if (!ok) break;
-          if (WIDE) {
-            if (mine)
-              bulk_load_1d((b_stage(s) + er.yoff) + lane * (er.tile_n * 2), yrow + n0,
-                           (uint32_t)min(er.tile_n, er.h_out - n0) * 2u, full_bar(s));
-          } else if (mine) {
-            for (int cb = 0; cb < ncb; ++cb)
-              bulk_load_1d((b_stage(s) + er.yoff) + cb * (kGatherRows * 128) + lane * 128,
-                           yrow + n0 + cb * kBoxCols, 128, full_bar(s));
-          }
+          // one copy per row: the stage's columns of Y row i, row-major behind the weights
+          if (mine)
+            bulk_load_1d((b_stage(s) + er.yoff) + lane * (er.tile_n * 2), yrow + n0,
+                         (uint32_t)min(er.tile_n, er.h_out - n0) * 2u, full_bar(s));
         }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -775,9 +776,9 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       const uint32_t idesc_g = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, kGatherRows, 0, 1);
       ok = __all_sync(0xffffffffu, mbar_wait(a_ready_bar, li & 1, &abort_s));
       for (int t = 0; t < er.nt_count && ok; ++t, ++it) {
-        const int s = it % nst, ab = it & (kExpAccBufs - 1);
+        const int s = it % nst, ab = it & (nacc - 1);
         bool got = mbar_wait(full_bar(s), (it / nst) & 1, &abort_s);
-        if (got) got = mbar_wait(tempty_bar(ab), ((it >> 2) & 1) ^ 1, &abort_s);
+        if (got) got = mbar_wait(tempty_bar(ab), ((it / nacc) & 1) ^ 1, &abort_s);
         ok = __all_sync(0xffffffffu, got);             // the whole warp goes on or gives up
         if (!ok) break;
         if (k_pad != ti.rank) {
@@ -806,13 +807,13 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
                 const uint64_t ad = smem_desc_sw128(b_stage(s) + mt * 2 * er.bstride + j * (kBoxRowsW * 128),
                                                     er.bstride, 1024);
                 const uint64_t bd = smem_desc_sw128(a_tile + (j >> 2) * (kTileM * 128) + (j & 3) * 32, 16, 1024);
-                umma_f16(tmem_base + ab * 128 + mt * kChainCols, ad, bd, idesc_g, j != 0);
+                umma_f16(tmem_base + ab * acc_cols + mt * kChainCols, ad, bd, idesc_g, j != 0);
               }
           } else {
             for (int j = 0; j < ksteps; ++j) {
               const uint64_t ad = smem_desc_sw128(a_tile + (j >> 2) * (kTileM * 128) + (j & 3) * 32, 16, 1024);
               const uint64_t bd = smem_desc_sw128(b_stage(s) + j * (kBoxRowsW * 128), er.bstride, 1024);
-              umma_f16(tmem_base + ab * 128, ad, bd, idesc, j != 0);
+              umma_f16(tmem_base + ab * acc_cols, ad, bd, idesc, j != 0);
             }
           }
           umma_commit(tfull_bar(ab));
@@ -883,15 +884,15 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       }
       const float scale = apply_scale ? Elem<T>::to_float(scales[ti.adapter]) : 1.f;
       for (int t = 0; t < er.nt_count; ++t, ++it) {
-        const int s = it % nst, ab = it & (kExpAccBufs - 1);
+        const int s = it % nst, ab = it & (nacc - 1);
         bool got = mbar_wait(full_bar(s), (it / nst) & 1, &abort_s);
-        if (got) got = mbar_wait(tfull_bar(ab), (it >> 2) & 1, &abort_s);
+        if (got) got = mbar_wait(tfull_bar(ab), (it / nacc) & 1, &abort_s);
         ok = __all_sync(0xffffffffu, got);
         if (!ok) break;
         tc_fence_after();
         if (warp == kExpEpiWarp0 && lane == 0) trace_stamp(src, it, 2);
         const int n0 = (er.nt_begin + t) * er.tile_n;
-        const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * 128;
+        const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * acc_cols;
         if (ti.gather) {
           // gathered rows, transposed product: this lane owns output column colt of the
           // stage's tile and gets the 16 row values of that column from tensor memory
@@ -939,9 +940,10 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
             uint32_t yv[kGatherRows];
             if (warp_live) {
               tmem_ld_32x16(tacc + j * 32, r);
-              const uint32_t yaddr = (b_stage(s) + er.yoff) + (colt >> 6) * (kGatherRows * 128) + (colt & 63) * 2;
+              const uint32_t yaddr = (b_stage(s) + er.yoff) + colt * 2;
+              const uint32_t ypitch = (uint32_t)er.tile_n * 2u;
   #pragma unroll
-              for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(yaddr + i * 128);
+              for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(yaddr + i * ypitch);
               tmem_ld_wait();
             }
             tc_fence_before();
@@ -966,24 +968,36 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         // consecutive rows: this warp's 32 rows x 64 columns = block j of the staged Y tile
         const uint32_t blk = (b_stage(s) + er.yoff) + j * (kTileM * 128);
         if (warp_live) {
-          // phase 1: lane = row.  out = y0 + scale * acc, rounded once, written back in place
-          uint32_t r0[32], r1[32];
-          uint4 yv[8];
-          tmem_ld_32x32(tacc + j * 64, r0);
-          tmem_ld_32x32(tacc + j * 64 + 32, r1);
+          // phase 1: lane = row.  out = y0 + scale * acc, rounded once, written back in place.
+          // The block's 64 accumulator columns come in four chunks of 16, each fetched while
+          // the previous one is combined with its two Y pieces: 32 accumulator registers live
+          // instead of 64 (with 64 the kernel sat on its register cap and spilled).
           const uint32_t rowaddr = blk + row * 128;
+          uint32_t ra[16], rb[16];
+          auto combine = [&](const uint32_t (&r)[16], int c16) {
 #pragma unroll
-          for (int c = 0; c < 8; ++c) yv[c] = lds128(rowaddr + ((c ^ (row & 7)) << 4));
+            for (int h = 0; h < 2; ++h) {
+              const int c = c16 * 2 + h;
+              const uint32_t a = rowaddr + ((c ^ (row & 7)) << 4);
+              float f[8];
+              unpack8<T>(lds128(a), f);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = fmaf(scale, __uint_as_float(r[h * 8 + e]), f[e]);
+              sts128(a, pack8<T>(f));
+            }
+          };
+          tmem_ld_32x16(tacc + j * 64, ra);
           tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            float f[8];
-            unpack8<T>(yv[c], f);
-#pragma unroll
-            for (int e = 0; e < 8; ++e)
-              f[e] = fmaf(scale, __uint_as_float(c < 4 ? r0[c * 8 + e] : r1[(c - 4) * 8 + e]), f[e]);
-            sts128(rowaddr + ((c ^ (row & 7)) << 4), pack8<T>(f));
-          }
+          tmem_ld_32x16(tacc + j * 64 + 16, rb);
+          combine(ra, 0);
+          tmem_ld_wait();
+          tmem_ld_32x16(tacc + j * 64 + 32, ra);
+          combine(rb, 1);
+          tmem_ld_wait();
+          tmem_ld_32x16(tacc + j * 64 + 48, rb);
+          combine(ra, 2);
+          tmem_ld_wait();
+          combine(rb, 3);
         }
         tc_fence_before();
         __syncwarp();
@@ -1119,14 +1133,52 @@ static long long* g_trace_ptr = nullptr;
 static int64_t g_trace_cap = 0;
 #endif
 
-static void size_rings(TileSource& src, int max_rank) {
+// ---- the tile table: launch-level choices per (kind of call, rank bound), measured on the
+// part and loaded by the host side (vlr_set_tile_table); the built-in defaults below are what
+// the table holds for a B200.  What follows from a tile's own rows and rank (copy box shapes,
+// K blocks or column blocks per stage) is derived in the kernels from the stage size.
+constexpr int kMaxTileChoices = 16;
+static vlr_tile_choice_t g_choices[kMaxTileChoices] = {
+    {64, 1, 4, 4, 32, 0}, {128, 1, 3, 3, 32, 0}, {64, 0, 4, 4, 32, 0}, {128, 0, 3, 3, 32, 0}};
+static int g_n_choices = 4;
+
+static bool choice_ok(const vlr_tile_choice_t& c) {
+  const bool stages_ok = c.shrink_stages >= 2 && c.shrink_stages <= 4 && c.expand_stages >= 3 &&
+                         c.expand_stages <= 4;
+  // a shrink stage must hold one K block of a full tile at the entry's largest rank, an expand
+  // stage two 64-column blocks (weights + Y rows)
+  const int pad = (c.max_rank + 15) & ~15;
+  const bool fits = kRingBytes / c.shrink_stages >= (kTileM + pad) * 128 &&
+                    kRingBytes / c.expand_stages >= 2 * (kTileM + pad) * 128;
+  const bool rows_ok = c.small_call_rows == 32 || c.small_call_rows == 64 || c.small_call_rows == 128;
+  return c.max_rank >= 8 && c.max_rank <= kMaxRank && (c.step == 0 || c.step == 1) && stages_ok && fits &&
+         rows_ok;
+}
+
+static const vlr_tile_choice_t* find_choice(int step, int max_rank) {
+  const vlr_tile_choice_t* best = nullptr;
+  for (int i = 0; i < g_n_choices; ++i) {
+    const vlr_tile_choice_t& c = g_choices[i];
+    if (c.step == step && c.max_rank >= max_rank && (best == nullptr || c.max_rank < best->max_rank)) best = &c;
+  }
+  return best;
+}
+
+static void size_rings(TileSource& src, int max_rank, bool step) {
   if (max_rank <= 0 || max_rank > kMaxRank) max_rank = kMaxRank;
   const int pad = (max_rank + 15) & ~15;
   src.max_rank = max_rank;
-  src.shrink_stages = pad <= 64 ? 4 : 3;               // 48 KB or 64 KB per stage: two K blocks of a full tile
+  const vlr_tile_choice_t* c = find_choice(step ? 1 : 0, max_rank);
+  // without an entry: 48 KB stages while a full tile's two K blocks fit, else 64 KB
+  src.shrink_stages = c ? c->shrink_stages : (pad <= 64 ? 4 : 3);
+  src.exp_stages = c ? c->expand_stages : (pad <= 64 ? 4 : 3);
   src.shrink_stage_bytes = kRingBytes / src.shrink_stages;
-  src.exp_stages = pad <= 64 ? 4 : 3;                  // 48 KB or 64 KB per stage
   src.exp_stage_bytes = kRingBytes / src.exp_stages;
+}
+
+static int small_call_rows(int max_rank) {
+  const vlr_tile_choice_t* c = find_choice(0, max_rank);
+  return c ? c->small_call_rows : 32;
 }
 
 template <typename T>
@@ -1144,6 +1196,8 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
       cudaError_t r = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
       if (e == cudaSuccess) e = r;
     };
+    set((const void*)atmm_shrink_kernel<__half, 2>, kShrinkSmem);
+    set((const void*)atmm_shrink_kernel<__nv_bfloat16, 2>, kShrinkSmem);
     set((const void*)atmm_shrink_kernel<__half, 3>, kShrinkSmem);
     set((const void*)atmm_shrink_kernel<__half, 4>, kShrinkSmem);
     set((const void*)atmm_shrink_kernel<__nv_bfloat16, 3>, kShrinkSmem);
@@ -1173,7 +1227,7 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
 #endif
   const bool step = src.plan != nullptr;
   // rank bound: the caller's hint in a step, the width of the rank-side buffer otherwise
-  size_rings(src, step ? src.max_rank : (h_in >= h_out ? h_out : h_in));
+  size_rings(src, step ? src.max_rank : (h_in >= h_out ? h_out : h_in), step);
   int rc;
   if (h_in >= h_out) {
     if (!step && (rc = make_map_set(&maps, x, T_rows, w, w_cells, h_in, dtype)) != VLR_OK) return rc;
@@ -1186,8 +1240,11 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
     if (src.shrink_stages == 4)
       atmm_shrink_kernel<T, 4><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
                                                                         h_in, h_out, acc);
-    else
+    else if (src.shrink_stages == 3)
       atmm_shrink_kernel<T, 3><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
+                                                                        h_in, h_out, acc);
+    else
+      atmm_shrink_kernel<T, 2><<<grid, kThreads, kShrinkSmem, stream>>>(maps, (T*)y, (const T*)x, src,
                                                                         h_in, h_out, acc);
   } else {
     if (!step && (rc = make_map_set(&maps, y, T_rows, w, w_cells, h_out, dtype)) != VLR_OK) return rc;
@@ -1199,18 +1256,15 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
     const int64_t items = max_tiles * n_problems * src.nsplit;
     const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
     const int sc = (flags & VLR_ATMM_APPLY_SCALE) ? 1 : 0;
-    if (src.exp_stages == 4 && !src.wide_gather)
-      atmm_expand_kernel<T, 4, false><<<grid, kExpThreads, kExpSmem, stream>>>(
-          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
-    else if (src.exp_stages == 4)
-      atmm_expand_kernel<T, 4, true><<<grid, kExpThreads, kExpSmem, stream>>>(
-          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
-    else if (!src.wide_gather)
-      atmm_expand_kernel<T, 3, false><<<grid, kExpThreads, kExpSmem, stream>>>(
-          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
-    else
-      atmm_expand_kernel<T, 3, true><<<grid, kExpThreads, kExpSmem, stream>>>(
-          maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc);
+#define VLR_EXPAND_LAUNCH(NST, WIDE)                                                  \
+  atmm_expand_kernel<T, NST, WIDE><<<grid, kExpThreads, kExpSmem, stream>>>(           \
+      maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc)
+    if (src.exp_stages == 4) {
+      if (src.wide_gather) VLR_EXPAND_LAUNCH(4, true); else VLR_EXPAND_LAUNCH(4, false);
+    } else {
+      if (src.wide_gather) VLR_EXPAND_LAUNCH(3, true); else VLR_EXPAND_LAUNCH(3, false);
+    }
+#undef VLR_EXPAND_LAUNCH
   }
   return launch_status();
 }
@@ -1260,7 +1314,7 @@ extern "C" int vlr_atmm(void* y, const void* x, const void* w, const int64_t* a_
   // into 32-row tiles it occupies four times as many SMs, and a stage holds several K blocks.
   src.tile_rows = kTileM;
   if (!expand && !(flags & VLR_ATMM_FULL_TILES) && T / kTileM + num_problems <= sm_count() / 2)
-    src.tile_rows = 32;
+    src.tile_rows = small_call_rows((int)narrow);
   const int64_t max_tiles = T / src.tile_rows + num_problems;
   return atmm_launch(y, x, w, lora_scales, src, max_tiles, T, (int)h_in, (int)h_out, w_cells, dtype,
                      flags, (cudaStream_t)stream, 1);
@@ -1276,6 +1330,31 @@ extern "C" int vlr_device_status(int reset) {
   const int d = vlr::bgmv_decode_status(reset);
   if (d < 0) return -1;
   return v | d;
+}
+
+extern "C" int vlr_set_tile_table(const vlr_tile_choice_t* entries, int n) {
+  if (n < 0 || n > vlr::kMaxTileChoices) return VLR_ERR_RANGE;
+  if (n > 0 && !entries) return VLR_ERR_NULL;
+  for (int i = 0; i < n; ++i)
+    if (!vlr::choice_ok(entries[i])) return VLR_ERR_RANGE;
+  for (int i = 0; i < n; ++i) vlr::g_choices[i] = entries[i];
+  vlr::g_n_choices = n;
+  return VLR_OK;
+}
+
+extern "C" int vlr_get_tile_choice(int step, int max_rank, vlr_tile_choice_t* out) {
+  if (!out) return VLR_ERR_NULL;
+  if (max_rank <= 0 || max_rank > vlr::kMaxRank) max_rank = vlr::kMaxRank;
+  vlr::TileSource src{};
+  vlr::size_rings(src, max_rank, step != 0);
+  const vlr_tile_choice_t* c = vlr::find_choice(step ? 1 : 0, max_rank);
+  out->max_rank = c ? c->max_rank : max_rank;
+  out->step = step ? 1 : 0;
+  out->shrink_stages = src.shrink_stages;
+  out->expand_stages = src.exp_stages;
+  out->small_call_rows = c ? c->small_call_rows : 32;
+  out->reserved = 0;
+  return VLR_OK;
 }
 
 extern "C" int vlr_selftest_bounded_wait(int64_t budget_cycles, int32_t* dev_status,

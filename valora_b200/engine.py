@@ -19,14 +19,14 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from . import ops
+from . import ops, tile_table
 from .pool import AdapterPool
 
 
 class LoraStepEngine:
     def __init__(self, projections: Sequence[Tuple[str, int, int]], ranks: Sequence[int],
                  scalings: Sequence[float], dtype, device, layers: int, max_tokens: int,
-                 tile_m: int = 128, mma_min_rows: int = 16, gather_rows_per_tile: Optional[int] = None,
+                 tile_m: int = 128, mma_min_rows: Optional[int] = None, gather_rows_per_tile: Optional[int] = None,
                  alloc_activations: bool = True, gather_path: str = "mma",
                  wide_gather: Optional[bool] = None, input_of: Optional[Sequence[int]] = None,
                  share_pools_with: Optional["LoraStepEngine"] = None):
@@ -46,10 +46,14 @@ class LoraStepEngine:
         same resident weights, e.g. with other activation buffers)."""
         if gather_path not in ("mma", "simt"):
             raise ValueError("gather_path must be 'mma' or 'simt'")
+        # thresholds that are measured, not derived: from the tile table in force
+        self.table = tile_table.current()["engine"]
+        if mma_min_rows is None:
+            mma_min_rows = int(self.table["mma_min_rows"])
         self.gather_path = gather_path
         self.wide_gather = wide_gather
         if gather_rows_per_tile is None:
-            gather_rows_per_tile = 16 if gather_path == "mma" else 8
+            gather_rows_per_tile = int(self.table["gather_rows_per_tile"]) if gather_path == "mma" else 8
         if gather_path == "simt" and gather_rows_per_tile > 8:
             raise ValueError("the SIMT gather kernels take at most 8 rows per tile")
         if gather_path == "mma" and gather_rows_per_tile > 16:
@@ -167,7 +171,8 @@ class LoraStepEngine:
         if self.gather_path != "mma":
             return 0
         # adapters of rank 32 or less: let a gather stage of the expand take more columns
-        on = min(self.ranks) <= 32 if self.wide_gather is None else bool(self.wide_gather)
+        on = (min(self.ranks) < int(self.table["wide_gather_below_rank"]) if self.wide_gather is None
+              else bool(self.wide_gather))
         wide = ops.STEP_WIDE_GATHER_STAGES if on else 0
         return ops.STEP_GATHER_ON_TENSOR_CORES | wide
 

@@ -233,7 +233,7 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
     eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T, input_of=input_of)
     eng.randomize_weights(seed=b.seed)
     g = torch.Generator(device=dev)
-    g.manual_seed(b.seed)
+    g.manual_seed(b.seed + 7919)          # another stream than the weights'
     for l in range(layers):
         for p in range(len(b.projections)):
             if eng.input_of[p] == p:
