@@ -330,6 +330,29 @@ __device__ __forceinline__ SubLayout sub_layout(const TileInfo& ti, int n_pad, u
   return sl;
 }
 
+// Gather tiles, where the activations are at least eight K blocks wide: a gathered row is
+// fetched g K blocks at a time with ONE copy (a [1 row x g blocks x 64 columns] box of the 3-D
+// view of the activations), which lands as g consecutive 128-byte lines.  Token i then owns
+// the lines i*g .. i*g+g-1 of the stage's X region, line i*g+j holding its K block j - and the
+// MMA, which takes line L for row L of a 128-row operand, multiplies the whole region with the
+// weights of K block j into accumulator j.  Of accumulator j only the rows L with L % g == j
+// mean anything (the others paired a token's block with another block's weights); the epilogue
+// picks those and adds the g of them that belong to a token.  One sixteenth to a quarter of the
+// copy instructions of one-row, one-block copies, which is what bounded these tiles.
+//   g = 8 accumulators of 32 columns (rank <= 32), 4 of 64 (rank <= 64), 2 of 128
+// Stage: [X region, 16 * g lines][weights of block 0] .. [weights of block g-1]
+struct GatherLayout { int g, gsel, astr; uint32_t xbytes, wbytes; };
+__device__ __forceinline__ GatherLayout gather_layout(int n_pad) {
+  GatherLayout gl;
+  gl.astr = n_pad <= 32 ? 32 : (n_pad <= 64 ? 64 : 128);
+  gl.g = 256 / gl.astr;
+  gl.gsel = gl.g == 8 ? 2 : (gl.g == 4 ? 1 : 0);
+  gl.xbytes = (uint32_t)(kGatherRows * gl.g) * 128u;
+  gl.wbytes = (uint32_t)n_pad * 128u;
+  return gl;
+}
+constexpr int kGather3MinBlocks = 8;                   // K blocks an activation row must have for this form
+
 template <typename T, int NST>
 __global__ void __launch_bounds__(kThreads, 1)
 atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
@@ -408,11 +431,41 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       const int h_in = hw;
       const int n_pad = (ti.rank + 15) & ~15;
       const int kblocks = (h_in + kBoxCols - 1) / kBoxCols;
-      const SubLayout sl = sub_layout(ti, n_pad, stage_bytes);
-      const int nstages = (kblocks + sl.kbs - 1) / sl.kbs;
       const bool mine = ti.gather && lane < ti.rows;
       const int grow = mine ? grow_l : 0;
       if (lane < 8) prefetch_tensormap(lane < 3 ? &ms->act[lane] : lane < 7 ? &ms->w[lane - 3] : &ms->row);
+      if (lane >= 8 && lane < 11 && kblocks >= kGather3MinBlocks) prefetch_tensormap(&ms->row3[lane - 8]);
+      if (ti.gather && kblocks >= kGather3MinBlocks) {
+        // ---- gathered rows, g K blocks per copy (see gather_layout)
+        const GatherLayout gl = gather_layout(n_pad);
+        const int nstages = (kblocks + gl.g - 1) / gl.g;
+        for (int st = 0; st < nstages; ++st, ++kiter) {
+          if ((int)(kiter % nprod) != warp) continue;
+          const int s = kiter % nst;
+          const int kb0 = st * gl.g;
+          const int nsub = min(gl.g, kblocks - kb0);
+          if (lane == 0) {
+            ok = mbar_wait(empty_bar(s), ((kiter / nst) & 1) ^ 1, &abort_s);
+            if (ok) {
+              trace_stamp(src, kiter, 0);
+              // a box counts its full size, also where it reaches past the last K block (zero fill)
+              mbar_expect_tx(full_bar(s), (uint32_t)ti.rows * (uint32_t)gl.g * 128u + (uint32_t)nsub * gl.wbytes);
+              for (int j = 0; j < nsub; ++j)
+                load_w_rows(x_stage(s) + gl.xbytes + j * gl.wbytes, ms, (kb0 + j) * kBoxCols, (int)ti.wrow0, n_pad,
+                            full_bar(s));
+              trace_stamp(src, kiter, 3);
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);          // also orders expect_tx before the copies
+          if (!ok) break;
+          if (mine)
+            tma_load_3d(x_stage(s) + (uint32_t)(lane * gl.g) * 128u, &ms->row3[gl.gsel], 0, kb0, grow, full_bar(s));
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        continue;
+      }
+      const SubLayout sl = sub_layout(ti, n_pad, stage_bytes);
+      const int nstages = (kblocks + sl.kbs - 1) / sl.kbs;
       const uint32_t blk_bytes =
           (uint32_t)((ti.gather ? ti.rows : act_rows_loaded(ti.rows)) + n_pad) * 128u;
       for (int st = 0; st < nstages; ++st, ++kiter) {
@@ -473,6 +526,30 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         const int astr = acc_stride(n_pad), nacc = 256 / astr;
         ok = mbar_wait(tempty_bar(ab), ((li >> 1) & 1) ^ 1, &abort_s);
         if (ok) tc_fence_after();
+        if (ti.gather && kblocks >= kGather3MinBlocks) {
+          // K block j of a stage goes to accumulator j, the whole X region as the A operand
+          const GatherLayout gl = gather_layout(n_pad);
+          const int nstages = (kblocks + gl.g - 1) / gl.g;
+          for (int st = 0; st < nstages && ok; ++st, ++kiter) {
+            const int s = kiter % nst;
+            ok = mbar_wait(full_bar(s), (kiter / nst) & 1, &abort_s);
+            if (!ok) break;
+            trace_stamp(src, kiter, 1);
+            tc_fence_after();
+            const int nsub = min(gl.g, kblocks - st * gl.g);
+            const uint64_t ad = smem_desc_sw128(x_stage(s), 16, 1024);
+            uint64_t bd = smem_desc_sw128(x_stage(s) + gl.xbytes, 16, 1024);
+            for (int j = 0; j < nsub; ++j) {
+#pragma unroll
+              for (int k = 0; k < kBoxCols / 16; ++k)
+                umma_f16(tacc + (uint32_t)(j * gl.astr), ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc,
+                         (st > 0 || k > 0) ? 1u : 0u);
+              bd += (uint64_t)(gl.wbytes >> 4);
+            }
+            umma_commit(empty_bar(s));
+            trace_stamp(src, kiter, 2);
+          }
+        } else {
         const SubLayout sl = sub_layout(ti, n_pad, stage_bytes);
         const int nstages = (kblocks + sl.kbs - 1) / sl.kbs;
         uint32_t aoff = 0, first = (uint32_t)nacc;     // next accumulator chain; chains not yet started
@@ -503,6 +580,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
           umma_commit(empty_bar(s));
           trace_stamp(src, kiter, 2);
         }
+        }
         if (ok) umma_commit(tfull_bar(ab));
         ++li;
       }
@@ -529,40 +607,76 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         v_pitch = kMaxRank;
       }
       const int n_pad = (ti.rank + 15) & ~15;
-      // tile row held by this lane (gathered rows sit in slots 0..15: lane quarter 0)
-      const int trow = ti.gather ? (q == 0 && lane < kGatherRows ? lane : kTileM) : row;
-      const bool warp_live = ti.gather ? q == 0 : q * 32 < ti.rows;
-      if (warp_live) {
-        T* vrow = v + (int64_t)(trow < ti.rows ? (ti.gather ? grow_l : ti.row0 + trow) : 0) * v_pitch;
-        const int astr = acc_stride(n_pad), nacc = 256 / astr;
-        for (int c = 0; c < n_pad; c += 16) {
-          uint32_t r[16];
-          tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + c, r);
-          for (int a = 1; a < nacc; ++a) {
-            uint32_t p[16];
-            tmem_ld_32x16(tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256 + a * astr + c, p);
-            tmem_ld_wait();
+      // 16 finished sums of one row, columns c .. c+15, rounded once and stored (columns >= rank stay)
+      auto store16 = [&](T* vrow, int c, const uint32_t (&r)[16]) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(p[e]));
+        for (int h = 0; h < 2; ++h) {
+          const int col = c + h * 8;
+          if (col < ti.rank) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[h * 8 + e]);
+            if (accumulate) {
+              float old[8];
+              unpack8<T>(ldg128(vrow + col), old);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] += old[e];
+            }
+            stg128(vrow + col, pack8<T>(f));
           }
-          tmem_ld_wait();
-          if (trow < ti.rows) {
+        }
+      };
+      const uint32_t tbuf = tmem_base + ((uint32_t)(q * 32) << 16) + ab * 256;
+      if (ti.gather && (hw + kBoxCols - 1) / kBoxCols >= kGather3MinBlocks) {
+        // gathered rows fetched g K blocks per copy: this lane holds line L of the X region =
+        // K block jj of token tok; of accumulator a only the lines with jj == a count, and a
+        // token's result is the sum over its g lines (see gather_layout)
+        const GatherLayout gl = gather_layout(n_pad);
+        const int tok = row >> (gl.gsel + 1), jj = row & (gl.g - 1);
+        const int my_row = __shfl_sync(0xffffffffu, grow_l, tok & (kGatherRows - 1));
+        if (q * 32 < ti.rows * gl.g) {
+          T* vrow = v + (int64_t)(tok < ti.rows ? my_row : 0) * v_pitch;
+          for (int c = 0; c < n_pad; c += 16) {
+            uint32_t r[16];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int col = c + h * 8;
-              if (col < ti.rank) {
-                float f[8];
+            for (int e = 0; e < 16; ++e) r[e] = 0u;
+            for (int a = 0; a < gl.g; ++a) {
+              uint32_t p[16];
+              tmem_ld_32x16(tbuf + a * gl.astr + c, p);
+              tmem_ld_wait();
+              if (a == jj) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[h * 8 + e]);
-                if (accumulate) {
-                  float old[8];
-                  unpack8<T>(ldg128(vrow + col), old);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) f[e] += old[e];
-                }
-                stg128(vrow + col, pack8<T>(f));
+                for (int e = 0; e < 16; ++e) r[e] = p[e];
               }
             }
+            for (int o = 1; o < gl.g; o <<= 1) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e)
+                r[e] = __float_as_uint(__uint_as_float(r[e]) +
+                                       __uint_as_float(__shfl_xor_sync(0xffffffffu, r[e], o)));
+            }
+            if (jj == 0 && tok < ti.rows) store16(vrow, c, r);
+          }
+        }
+      } else {
+        // tile row held by this lane (gathered rows sit in slots 0..15: lane quarter 0)
+        const int trow = ti.gather ? (q == 0 && lane < kGatherRows ? lane : kTileM) : row;
+        const bool warp_live = ti.gather ? q == 0 : q * 32 < ti.rows;
+        if (warp_live) {
+          T* vrow = v + (int64_t)(trow < ti.rows ? (ti.gather ? grow_l : ti.row0 + trow) : 0) * v_pitch;
+          const int astr = acc_stride(n_pad), nacc = 256 / astr;
+          for (int c = 0; c < n_pad; c += 16) {
+            uint32_t r[16];
+            tmem_ld_32x16(tbuf + c, r);
+            for (int a = 1; a < nacc; ++a) {
+              uint32_t p[16];
+              tmem_ld_32x16(tbuf + a * astr + c, p);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(p[e]));
+            }
+            tmem_ld_wait();
+            if (trow < ti.rows) store16(vrow, c, r);
           }
         }
       }
@@ -1108,9 +1222,28 @@ int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int6
   return r == CUDA_SUCCESS ? VLR_OK : VLR_ERR_DRIVER;
 }
 
+// [rows][cols / 64][64] view of a row-major [rows, cols] tensor (cols % 64 == 0), box = one
+// row x kblocks consecutive 64-column blocks
+static int make_map_row3(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int kblocks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return VLR_ERR_DRIVER;
+  cuuint64_t dims[3] = {(cuuint64_t)kBoxCols, (cuuint64_t)(cols / kBoxCols), (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)kBoxCols * 2, (cuuint64_t)cols * 2};
+  cuuint32_t box[3] = {(cuuint32_t)kBoxCols, (cuuint32_t)kblocks, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dtype == VLR_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                  3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? VLR_OK : VLR_ERR_DRIVER;
+}
+
 int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, int64_t w_rows,
                  int64_t cols, int dtype) {
   int rc;
+  if (cols % kBoxCols == 0 && cols / kBoxCols >= 8)
+    for (int i = 0; i < 3; ++i)
+      if ((rc = make_map_row3(&set->row3[i], act, dtype, act_rows, cols, 2 << i)) != VLR_OK) return rc;
   for (int i = 0; i < 3; ++i)
     if ((rc = make_map_2d(&set->act[i], act, dtype, act_rows, cols, 32 << i)) != VLR_OK) return rc;
   for (int i = 0; i < 4; ++i)

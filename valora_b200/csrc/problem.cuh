@@ -17,6 +17,9 @@ struct alignas(128) MapSet {
   CUtensorMap act[3];   // boxes of 32 / 64 / 128 activation rows x 64 columns
   CUtensorMap w[4];     // boxes of 16 / 32 / 64 / 128 pool cells x 64 columns
   CUtensorMap row;      // one activation row x 64 columns (gathered rows)
+  CUtensorMap row3[3];  // one activation row x 2 / 4 / 8 consecutive 64-column blocks, as a 3-D view
+                        // [rows][cols / 64][64] of the activations (cols a multiple of 64, else unset):
+                        // the blocks land as consecutive 128-byte lines
 };
 
 struct alignas(128) StepProblem {
