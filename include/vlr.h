@@ -51,7 +51,9 @@ extern "C" {
 /* flags of vlr_atmm */
 #define VLR_ATMM_ACCUMULATE_SHRINK 1 /* shrink adds into y (reference epilogue beta = 1,
                                         atmm/valora/csrc/bgmv/bgmv_impl.cuh:174); default overwrites */
-#define VLR_ATMM_APPLY_SCALE 2       /* expand multiplies by lora_scales[adapter]; the reference
+#define VLR_ATMM_APPLY_SCALE 2       /* the call multiplies its result by lora_scales[adapter] in fp32
+                                        before the single rounding (an expand: the update; a shrink:
+                                        V' = s X A, what vlr_fused_proj consumes); the reference
                                         epilogue uses alpha = 1 (same file :174, :236) */
 #define VLR_ATMM_FULL_TILES 4        /* shrink: always cut segments into 128-row tiles.  Without it a
                                         call with few rows (T/128 + num_problems <= half the SMs) uses
@@ -135,7 +137,7 @@ int vlr_atmm(void* y, const void* x, const void* w,
  * rows in gather_rows.  counts[VLR_COUNT_INTS] receives the totals.
  * Capacities: perm, gather_rows: T; seg_*: min(T, n_adapters or T) + 1;
  * tiles: tiles_cap tiles of VLR_TILE_INTS int32.
- * Limits: tile_m <= 128 (one MMA tile), gather_rows_per_tile <= 16, else
+ * Limits: tile_m <= 128 (one MMA tile), gather_rows_per_tile <= 32, else
  * VLR_ERR_RANGE.  Four small launches; counts is written in full every call.
  */
 size_t vlr_pack_workspace_bytes(int64_t T, int64_t n_adapters);
@@ -176,6 +178,31 @@ int vlr_pack_static(const int64_t* tok_adapter, int64_t T, const int64_t* a_len,
  */
 int vlr_var_len_copy(const int64_t* old_start, const int64_t* len, const int64_t* old_loc,
                      const int64_t* new_start, int64_t* new_loc, int64_t n, void* stream);
+
+/*
+ * Base projection with the LoRA update folded into the same accumulator:
+ *     y[rows, :] = x[rows, :] W  +  v[rows, :r] B_a
+ * for the rows of the consecutive-row tiles of a packed batch (tiles / counts from
+ * vlr_pack: up to 128 rows of one adapter each), 256 output columns per work
+ * item.  v is the pre-scaled shrink result V' = s X A (vlr_atmm or the step's
+ * shrink with the scale applied), [T, v_pitch]; W is the base weight [h_in,
+ * h_out] row-major; B_a the adapter's r rows in the B-side pool (consecutive
+ * cells from a_loc_b[a_start_b[a] + r * slot_b]).  y is WRITTEN, never read:
+ * the read-modify-write of y that the expand needs disappears, and with it two
+ * thirds of the operator's HBM bytes.  Rows outside the consecutive-row tiles
+ * (gather rows, i.e. decode tokens) are not touched; they go through a plain
+ * base projection plus the gather expand.  h_in and h_out multiples of 64.
+ * In the reference the two halves are a torch.mm that writes q / k / v / o and
+ * dispatch_sgmm calls that read them back and add
+ * (valora/models/peft/lora_unordered_batch_infer.py:885, :967-988, :1568,
+ * :1611-1622; base weights valora/models/llama/layer_infer/
+ * transformer_layer_infer.py:42-50).  dev_status as in vlr_lora_step.
+ */
+int vlr_fused_proj(void* y, const void* x, const void* w_base, const void* v, int64_t v_pitch,
+                   const void* wb_pool, int64_t cells_b, const int64_t* a_start_b,
+                   const int64_t* a_loc_b, int64_t slot_b, const int32_t* tiles,
+                   const int32_t* counts, int64_t max_mma_tiles, int64_t T, int64_t h_in,
+                   int64_t h_out, int dtype, int32_t* dev_status, void* stream);
 
 /*
  * The tile table: what a launch of the tensor-core kernels is shaped like, per
@@ -290,7 +317,7 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
 /* or-ed into phase_mask: the gather tiles (rows that are not consecutive in the
  * batch, e.g. decode tokens) are processed by the two tensor-core launches, their
  * rows fetched with 128-byte 1-D bulk copies instead of tiled bulk copies; the
- * two SIMT gather launches are skipped.  gather_rows_per_tile must be <= 16 with
+ * two SIMT gather launches are skipped.  gather_rows_per_tile must be <= 32 with
  * this flag and <= 8 without it.  Plans need h_in and h_out multiples of 64. */
 #define VLR_STEP_GATHER_ON_TENSOR_CORES 16
 /* or-ed into phase_mask together with VLR_STEP_GATHER_ON_TENSOR_CORES: a gather

@@ -946,4 +946,68 @@ def test_step_reports_skipped_tiles_in_its_own_status_word(ops):
     with pytest.raises(RuntimeError):
         ops.Packer(64, 2, DEV, tile_m=256)                   # a tile is one MMA tile at most
     with pytest.raises(RuntimeError):
-        ops.Packer(64, 2, DEV, gather_rows_per_tile=32)
+        ops.Packer(64, 2, DEV, gather_rows_per_tile=64)
+
+
+# --------------------------------------------------------------------------- base projection with the expand folded in
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fused_projection_matches_base_plus_lora(ops, dtype):
+    """y = x W + s (x A) B in one pass over y (written, never read) for the rows of the
+    consecutive-row tiles; rows of gather tiles keep what they held.  Checked against
+    fp32 torch on the same V' (the kernel's arithmetic) and against the operator's fp32
+    truth with nothing rounded on the way (V' is a 16-bit tensor, scaled before its one
+    rounding by the shrink's apply_scale)."""
+    h_in, h_out = 512, 768
+    ranks = [8, 16, 64, 128, 32]
+    seg_len = [300, 129, 5, 64, 17, 200, 3]
+    seg_ad = [1, 0, 4, 2, 1, 3, 0]
+    tok = np.repeat(seg_ad, seg_len).astype(np.int64)
+    T = tok.shape[0]
+    A, B = rand_lora(ranks, h_in, h_out, dtype, n_slots=2, seed=51, wstd=0.02)
+    a_start, a_len, a_loc, total = build_tables(ranks, 2, shuffle=True, contiguous_slots=True, seed=52)
+    slot = 1
+    wa = fill_pool_a(A, ranks, a_start, a_loc, total, h_in, dtype)
+    wb = fill_pool_b(B, ranks, a_start, a_loc, total, h_out, dtype, layout="rows")
+    g = torch.Generator().manual_seed(53)
+    x = torch.randn(T, h_in, generator=g).to(dtype)
+    W = (torch.randn(h_in, h_out, generator=g) * 0.05).to(dtype)
+    scales = torch.tensor([16.0 / r for r in ranks]).to(dtype)
+    dev = lambda t: t.to(DEV)
+    packer = ops.Packer(T, len(ranks), DEV)
+    alen_d = t64(a_len, DEV)
+    # V' from the shrink entry point with the scale applied (problem table in batch order)
+    pk0 = packer.pack(torch.from_numpy(tok).to(DEV), alen_d, sort=False)
+    P = pk0.host_counts()["P"]
+    vp = torch.zeros(T, 128, dtype=dtype, device=DEV)
+    ops.atmm(vp, dev(x), dev(wa).view(total, 1, h_in), t64(a_start, DEV), alen_d, t64(a_loc, DEV),
+             torch.from_numpy(tok).to(DEV), slot, dev(scales), pk0.seg_len.clone(), pk0.seg_rank.clone(),
+             pk0.seg_adapter.clone(), pk0.seg_start.clone(), None, P, apply_scale=True)
+    torch.cuda.synchronize()
+    v_truth = torch.zeros(T, 128)
+    for t in range(T):
+        a = int(tok[t])
+        v_truth[t, :ranks[a]] = (x[t].float() @ A[slot][a].float()) * float(scales[a])
+    assert _err(vp, v_truth) <= TOL
+    # the fused projection on the sorted schedule
+    pk = packer.pack(torch.from_numpy(tok).to(DEV), alen_d, sort=True)
+    c = pk.host_counts()
+    assert c["n_mma"] > 0 and c["n_gather"] > 0
+    y = torch.full((T, h_out), float("nan"), dtype=dtype, device=DEV)
+    ops.fused_proj(y, dev(x), dev(W), vp, dev(wb), t64(a_start, DEV), t64(a_loc, DEV), slot, pk)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    in_gather = np.isin(tok, [4]) | (np.arange(T) >= T - 3)          # the 5-row and the 3-row run
+    yc = y.cpu()
+    assert torch.isnan(yc[torch.from_numpy(in_gather)].float()).all()     # untouched
+    rows = torch.from_numpy(~in_gather)
+    same_v = x.float() @ W.float()
+    truth = same_v.clone()
+    vpc = vp.cpu().float()
+    for t in range(T):
+        a = int(tok[t])
+        same_v[t] += vpc[t, :ranks[a]] @ B[slot][a].float()
+        truth[t] += ((x[t].float() @ A[slot][a].float()) @ B[slot][a].float()) * float(scales[a])
+    assert _err(y[dev(rows)], same_v[rows]) <= TOL
+    assert own_error(y[dev(rows)], same_v[rows]) <= 1e-4            # fp32 accumulation order only
+    assert _err(y[dev(rows)], truth[rows]) <= TOL
+    assert own_error(y[dev(rows)], truth[rows]) <= OWN_TOL

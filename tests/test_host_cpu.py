@@ -44,8 +44,8 @@ def test_host_validation_codes_without_a_gpu():
                              null) == -1
     assert lib.vlr_pack(one, 10, one, 8, 1, 256, 16, 8, one, one, one, one, one, one, 10, one, one,
                         one, 1 << 20, null) == -6                                               # tile_m > 128
-    assert lib.vlr_pack_static(one, 10, one, 8, 1, 128, 16, 32, one, one, one, one, one, one, 10, one, one,
-                               null) == -6                                                      # 32 gathered rows per tile
+    assert lib.vlr_pack_static(one, 10, one, 8, 1, 128, 16, 64, one, one, one, one, one, one, 10, one, one,
+                               null) == -6                                                      # 64 gathered rows per tile
     assert lib.vlr_pack_static(one, 9000, one, 8, 1, 128, 16, 8, one, one, one, one, one, one, 10, one, one,
                                null) == -9                                                      # beyond the built-in scratch
     assert lib.vlr_selftest_bounded_wait(0, null, null, null) == -6
@@ -112,3 +112,37 @@ def test_pool_allocator_matches_reference_semantics():
     assert np.array_equal(run, np.arange(run[0], run[0] + 12)) and np.all(state[run] == 1)
     with pytest.raises(Exception):
         pool.alloc(1000)
+
+
+def test_launcher_follows_the_tile_table():
+    """The launch-level choices come from the committed table (valora_b200/tile_table.json,
+    written by the autotuner): for every entry the launcher reports exactly the entry's
+    values, rank bounds in between resolve to the next entry up, a replaced table is
+    honoured at once and a table the kernels cannot run is refused."""
+    import json
+    from valora_b200 import tile_table
+    lib = _lib.load()
+    t = tile_table.load(tile_table.DEFAULT_PATH)
+    assert t["gpu"] and len(t["entries"]) >= 4
+    tile_table.apply(lib, t)
+    for e in t["entries"]:
+        got = tile_table.choice(lib, bool(e["step"]), e["max_rank"])
+        assert {k: got[k] for k in ("shrink_stages", "expand_stages", "small_call_rows")} == \
+            {k: e[k] for k in ("shrink_stages", "expand_stages", "small_call_rows")}, e
+    by = {(e["step"], e["max_rank"]): e for e in t["entries"]}
+    assert tile_table.choice(lib, True, 16)["shrink_stages"] == by[(1, 64)]["shrink_stages"]
+    assert tile_table.choice(lib, True, 96)["shrink_stages"] == by[(1, 128)]["shrink_stages"]
+    assert tile_table.choice(lib, False, 8)["small_call_rows"] == by[(0, 64)]["small_call_rows"]
+    other = json.loads(json.dumps(t))
+    other["entries"][0].update(shrink_stages=2, small_call_rows=64)
+    tile_table.apply(lib, other)
+    e0 = other["entries"][0]
+    assert tile_table.choice(lib, bool(e0["step"]), e0["max_rank"])["shrink_stages"] == 2
+    bad = json.loads(json.dumps(t))
+    bad["entries"][1].update(expand_stages=4)            # rank 128 does not fit 48 KB expand stages
+    with pytest.raises(RuntimeError):
+        tile_table.apply(lib, bad)
+    tile_table.apply(lib, t)
+    assert tile_table.choice(lib, bool(e0["step"]), e0["max_rank"])["shrink_stages"] == t["entries"][0]["shrink_stages"]
+    eng = t["engine"]
+    assert eng["gather_rows_per_tile"] <= 32 and eng["mma_min_rows"] >= 1

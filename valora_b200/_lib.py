@@ -20,6 +20,8 @@ _SIGS = {
     "vlr_error_string": (ctypes.c_char_p, [c_int]),
     "vlr_set_device": (c_int, [c_int]),
     "vlr_selftest_bounded_wait": (c_int, [c_i64, c_vp, c_vp, c_vp]),
+    "vlr_fused_proj": (c_int, [c_vp, c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_vp, c_vp, c_i64, c_vp, c_vp, c_i64,
+                               c_i64, c_i64, c_i64, c_int, c_vp, c_vp]),
     "vlr_set_tile_table": (c_int, [c_vp, c_int]),
     "vlr_get_tile_choice": (c_int, [c_int, c_int, c_vp]),
     "vlr_device_status": (c_int, [c_int]),

@@ -43,7 +43,10 @@ constexpr int kShrinkFetchWarp = kShrinkEpiWarp0 + 4;   // warp 8: draws work it
 constexpr int kThreads = 32 * (kShrinkFetchWarp + 1);
 constexpr int kBoxRowsW = 16;        // weight rows per TMA box
 constexpr int kBoxCols = 64;         // 64 two-byte elements = 128 bytes = swizzle span
-constexpr int kGatherRows = 16;      // rows of a gather tile (row slots 0, 8, ..., 120)
+constexpr int kGatherRows = 32;      // rows of a gather tile, at most (one producer lane per row)
+// Tiles of 16 rows or fewer are laid out for 16 (N = 16 in the expand's transposed product, twice
+// the K blocks per row copy in the shrink), the others for 32.
+__device__ __forceinline__ int gather_cap(int rows) { return rows <= 16 ? 16 : 32; }
 
 struct TileInfo {
   int valid;
@@ -323,7 +326,7 @@ constexpr int kShrinkSmem = 1024 + kRingBytes + 512 + 512 + kTileM * 128;   // +
 struct SubLayout { uint32_t xbytes, sub; int kbs; };
 __device__ __forceinline__ SubLayout sub_layout(const TileInfo& ti, int n_pad, uint32_t stage_bytes) {
   SubLayout sl;
-  sl.xbytes = (uint32_t)(ti.gather ? kGatherRows : act_rows_loaded(ti.rows)) * 128u;
+  sl.xbytes = (uint32_t)(ti.gather ? gather_cap(ti.rows) : act_rows_loaded(ti.rows)) * 128u;
   sl.sub = sl.xbytes + (uint32_t)n_pad * 128u;
   const int k = (int)(stage_bytes / sl.sub);
   sl.kbs = k < 1 ? 1 : (k > kShrinkMaxSub ? kShrinkMaxSub : k);
@@ -339,15 +342,17 @@ __device__ __forceinline__ SubLayout sub_layout(const TileInfo& ti, int n_pad, u
 // mean anything (the others paired a token's block with another block's weights); the epilogue
 // picks those and adds the g of them that belong to a token.  One sixteenth to a quarter of the
 // copy instructions of one-row, one-block copies, which is what bounded these tiles.
-//   g = 8 accumulators of 32 columns (rank <= 32), 4 of 64 (rank <= 64), 2 of 128
-// Stage: [X region, 16 * g lines][weights of block 0] .. [weights of block g-1]
+//   g = 8 accumulators of 32 columns (rank <= 32), 4 of 64 (rank <= 64), 2 of 128 - and no
+//   more than the 128 lines of the operand allow: 8 for tiles of up to 16 rows, else 4
+// Stage: [X region, cap * g lines][weights of block 0] .. [weights of block g-1]
 struct GatherLayout { int g, gsel, astr; uint32_t xbytes, wbytes; };
-__device__ __forceinline__ GatherLayout gather_layout(int n_pad) {
+__device__ __forceinline__ GatherLayout gather_layout(int n_pad, int rows) {
   GatherLayout gl;
+  const int cap = gather_cap(rows);
   gl.astr = n_pad <= 32 ? 32 : (n_pad <= 64 ? 64 : 128);
-  gl.g = 256 / gl.astr;
+  gl.g = min(256 / gl.astr, kTileM / cap);
   gl.gsel = gl.g == 8 ? 2 : (gl.g == 4 ? 1 : 0);
-  gl.xbytes = (uint32_t)(kGatherRows * gl.g) * 128u;
+  gl.xbytes = (uint32_t)(cap * gl.g) * 128u;
   gl.wbytes = (uint32_t)n_pad * 128u;
   return gl;
 }
@@ -437,7 +442,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       if (lane >= 8 && lane < 11 && kblocks >= kGather3MinBlocks) prefetch_tensormap(&ms->row3[lane - 8]);
       if (ti.gather && kblocks >= kGather3MinBlocks) {
         // ---- gathered rows, g K blocks per copy (see gather_layout)
-        const GatherLayout gl = gather_layout(n_pad);
+        const GatherLayout gl = gather_layout(n_pad, ti.rows);
         const int nstages = (kblocks + gl.g - 1) / gl.g;
         for (int st = 0; st < nstages; ++st, ++kiter) {
           if ((int)(kiter % nprod) != warp) continue;
@@ -528,7 +533,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         if (ok) tc_fence_after();
         if (ti.gather && kblocks >= kGather3MinBlocks) {
           // K block j of a stage goes to accumulator j, the whole X region as the A operand
-          const GatherLayout gl = gather_layout(n_pad);
+          const GatherLayout gl = gather_layout(n_pad, ti.rows);
           const int nstages = (kblocks + gl.g - 1) / gl.g;
           for (int st = 0; st < nstages && ok; ++st, ++kiter) {
             const int s = kiter % nst;
@@ -608,6 +613,9 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
       }
       const int n_pad = (ti.rank + 15) & ~15;
       // 16 finished sums of one row, columns c .. c+15, rounded once and stored (columns >= rank stay)
+      const float vscale = src.shrink_scales != nullptr
+                               ? Elem<T>::to_float(reinterpret_cast<const T*>(src.shrink_scales)[ti.adapter])
+                               : 1.f;
       auto store16 = [&](T* vrow, int c, const uint32_t (&r)[16]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -615,7 +623,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
           if (col < ti.rank) {
             float f[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[h * 8 + e]);
+            for (int e = 0; e < 8; ++e) f[e] = vscale * __uint_as_float(r[h * 8 + e]);
             if (accumulate) {
               float old[8];
               unpack8<T>(ldg128(vrow + col), old);
@@ -631,7 +639,7 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         // gathered rows fetched g K blocks per copy: this lane holds line L of the X region =
         // K block jj of token tok; of accumulator a only the lines with jj == a count, and a
         // token's result is the sum over its g lines (see gather_layout)
-        const GatherLayout gl = gather_layout(n_pad);
+        const GatherLayout gl = gather_layout(n_pad, ti.rows);
         const int tok = row >> (gl.gsel + 1), jj = row & (gl.g - 1);
         const int my_row = __shfl_sync(0xffffffffu, grow_l, tok & (kGatherRows - 1));
         if (q * 32 < ti.rows * gl.g) {
@@ -736,8 +744,12 @@ __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileI
   r.bstride = (uint32_t)(((ti.rank + 15) & ~15) * 128);
   r.ncbt = (ti.gather && ti.rank <= 64) ? 4 : 2;
   if (WIDE && ti.gather) {
-    const int n = (int)((uint32_t)src.exp_stage_bytes / (r.bstride + kGatherRows * 128)) & ~1;
-    r.ncbt = n < 2 ? 2 : (n > 16 ? 16 : n);
+    // as many blocks as the stage holds (weights + the rows' pieces), an even number; a chain of
+    // 128 columns takes as many accumulator columns as the tile has row slots, 128 in all
+    const int cap = gather_cap(ti.rows);
+    const int n = (int)((uint32_t)src.exp_stage_bytes / (r.bstride + cap * 128)) & ~1;
+    const int most = 256 / cap;
+    r.ncbt = n < 2 ? 2 : (n > most ? most : n);
   }
   r.tile_n = r.ncbt * kBoxCols;
   r.yoff = (uint32_t)r.ncbt * r.bstride;
@@ -756,7 +768,6 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_s;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int grow_s[kExpEpiWarps][kGatherRows];    // rows of the gather tile an epilogue warp works on
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t total = total_items(src);
@@ -887,7 +898,8 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       const int k_pad = (ti.rank + 15) & ~15;
       const int ksteps = k_pad / 16;
       const uint32_t idesc = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, er.tile_n, 1);
-      const uint32_t idesc_g = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, kGatherRows, 0, 1);
+      const int gcap = gather_cap(ti.rows);            // N of the transposed product = row slots
+      const uint32_t idesc_g = instr_desc_f16(std::is_same<T, __nv_bfloat16>::value, gcap, 0, 1);
       ok = __all_sync(0xffffffffu, mbar_wait(a_ready_bar, li & 1, &abort_s));
       for (int t = 0; t < er.nt_count && ok; ++t, ++it) {
         const int s = it % nst, ab = it & (nacc - 1);
@@ -911,11 +923,11 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         if (lane == 0) {
           trace_stamp(src, it, 1);
           if (ti.gather) {
-            // D^T[128 cols x 16 rows] = B^T[128 x k] * V^T[k x 16], one chain per 128 columns:
+            // D^T[128 cols x N rows] = B^T[128 x k] * V^T[k x N], one chain per 128 columns:
             // A operand = the staged B tile read MN-major (two 64-column blocks bstride
-            // apart), B operand = the V rows, K-major, N = 16.
-            // accumulator chains 32 columns apart, or 16 where a stage may hold eight of them
-            constexpr int kChainCols = WIDE ? 16 : 32;
+            // apart), B operand = the V rows, K-major, N = 16 or 32 row slots; a chain takes N
+            // accumulator columns
+            const int kChainCols = gcap;
             for (int mt = 0; mt < (er.ncbt >> 1); ++mt)
               for (int j = 0; j < ksteps; ++j) {
                 const uint64_t ad = smem_desc_sw128(b_stage(s) + mt * 2 * er.bstride + j * (kBoxRowsW * 128),
@@ -960,11 +972,9 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         ti = sl->ti;
         hw = sl->h;
         yb = sl->ybase;
-        grow_l = sl->grow[lane & (kGatherRows - 1)];
-        if (lane < kGatherRows) grow_s[warp][lane] = grow_l;    // this warp's copy: the slot is recycled
+        grow_l = sl->grow[lane & (kGatherRows - 1)];   // lane i keeps row i of a gather tile
         tile_release(feed, ik);
       }
-      const int* grow = grow_s[warp];
       if (ti.valid < 0) break;
       if (!ti.valid) continue;
       const ExpRange er = exp_range<WIDE>(src, ti, hw);
@@ -1008,71 +1018,46 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
         const int n0 = (er.nt_begin + t) * er.tile_n;
         const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + ab * acc_cols;
         if (ti.gather) {
-          // gathered rows, transposed product: this lane owns output column colt of the
-          // stage's tile and gets the 16 row values of that column from tensor memory
-          if constexpr (WIDE) {
-            // warp (q, j) takes the chains j, j + 2, ... of 128 columns; within a chain this lane
-            // owns column q * 32 + lane.  Row-major Y tile, tile_n columns wide.  The accumulator
-            // is handed back once this warp's last chain is in registers.
-            const int nchains = er.ncbt >> 1;
-            const uint32_t ytile = b_stage(s) + er.yoff;
-            const uint32_t ypitch = (uint32_t)er.tile_n * 2u;
-            for (int mt = j; mt < nchains; mt += 2) {
-              const int colt = mt * 128 + q * 32 + lane;
-              const int col = n0 + colt;
-              uint32_t r[kGatherRows];
-              uint32_t yv[kGatherRows];
-              tmem_ld_32x16(tacc + mt * 16, r);
+          // gathered rows, transposed product: warp (q, j) takes the chains j, j + 2, ... of 128
+          // columns; within a chain this lane owns column q * 32 + lane and gets the row values
+          // of that column from tensor memory, 16 rows at a time.  Row-major Y tile, tile_n
+          // columns wide.  The accumulator is handed back once this warp's last chunk is in
+          // registers.
+          const int nhalf = gather_cap(ti.rows) >> 4;
+          const int cs = 16 * nhalf;                   // accumulator columns per chain
+          const int nchains = er.ncbt >> 1;
+          const uint32_t ytile = b_stage(s) + er.yoff;
+          const uint32_t ypitch = (uint32_t)er.tile_n * 2u;
+          for (int mt = j; mt < nchains; mt += 2) {
+            const int colt = mt * 128 + q * 32 + lane;
+            const int col = n0 + colt;
+            for (int half = 0; half < nhalf; ++half) {
+              uint32_t r[16];
+              uint32_t yv[16];
+              tmem_ld_32x16(tacc + mt * cs + half * 16, r);
 #pragma unroll
-              for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(ytile + i * ypitch + colt * 2);
+              for (int i = 0; i < 16; ++i) yv[i] = lds16(ytile + (half * 16 + i) * ypitch + colt * 2);
               tmem_ld_wait();
-              if (mt + 2 >= nchains) {
+              if (mt + 2 >= nchains && half == nhalf - 1) {
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(ab));
               }
-              if (col < h_out) {
 #pragma unroll
-                for (int i = 0; i < kGatherRows; ++i) {
-                  if (i < ti.rows) {
-                    const uint16_t y16 = (uint16_t)yv[i];
-                    const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
-                    y[(int64_t)grow[i] * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
-                  }
+              for (int i = 0; i < 16; ++i) {
+                const int gi = __shfl_sync(0xffffffffu, grow_l, half * 16 + i);   // row i of this half
+                if (col < h_out && half * 16 + i < ti.rows) {
+                  const uint16_t y16 = (uint16_t)yv[i];
+                  const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
+                  y[(int64_t)gi * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
                 }
               }
             }
-            if (j >= nchains) {                        // a warp without a chain in this stage
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(tempty_bar(ab));
-            }
-          } else {
-            const int colt = j * 128 + q * 32 + lane;
-            const int col = n0 + colt;
-            uint32_t r[kGatherRows];
-            uint32_t yv[kGatherRows];
-            if (warp_live) {
-              tmem_ld_32x16(tacc + j * 32, r);
-              const uint32_t yaddr = (b_stage(s) + er.yoff) + colt * 2;
-              const uint32_t ypitch = (uint32_t)er.tile_n * 2u;
-  #pragma unroll
-              for (int i = 0; i < kGatherRows; ++i) yv[i] = lds16(yaddr + i * ypitch);
-              tmem_ld_wait();
-            }
+          }
+          if (j >= nchains) {                          // a warp without a chain in this stage
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(ab));
-            if (warp_live && col < h_out) {
-  #pragma unroll
-              for (int i = 0; i < kGatherRows; ++i) {
-                if (i < ti.rows) {
-                  const uint16_t y16 = (uint16_t)yv[i];
-                  const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
-                  y[(int64_t)grow[i] * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
-                }
-              }
-            }
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(empty_bar(s));
@@ -1168,6 +1153,8 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
   }
   if (threadIdx.x == 0 && abort_s) raise_status(src, 1);
 }
+
+#include "fused_proj.cuh"
 
 // One CTA, one thread: wait on an mbarrier that nothing ever arrives on, with a budget of
 // `budget_cycles`, and report the give-up like the kernels above do.  Exercises the bounded
@@ -1442,6 +1429,7 @@ extern "C" int vlr_atmm(void* y, const void* x, const void* w, const int64_t* a_
   src.a_loc = a_loc;
   src.slot = qkvo;
   src.mode = 0;
+  if (!expand && (flags & VLR_ATMM_APPLY_SCALE)) src.shrink_scales = lora_scales;
   // every problem with m rows has ceil(m / tile rows) tiles; sum <= T / tile rows + num_problems.
   // A shrink with few rows is a few CTAs each walking all of K at the latency of a stage; cut
   // into 32-row tiles it occupies four times as many SMs, and a stage holds several K blocks.
@@ -1463,6 +1451,70 @@ extern "C" int vlr_device_status(int reset) {
   const int d = vlr::bgmv_decode_status(reset);
   if (d < 0) return -1;
   return v | d;
+}
+
+extern "C" int vlr_fused_proj(void* y, const void* x, const void* w_base, const void* v, int64_t v_pitch,
+                              const void* wb_pool, int64_t cells_b, const int64_t* a_start_b,
+                              const int64_t* a_loc_b, int64_t slot_b, const int32_t* tiles,
+                              const int32_t* counts, int64_t max_mma_tiles, int64_t T, int64_t h_in,
+                              int64_t h_out, int dtype, int32_t* dev_status, void* stream) {
+  using namespace vlr;
+  if (T == 0) return VLR_OK;
+  if (!y || !x || !w_base || !v || !wb_pool || !a_start_b || !a_loc_b || !tiles || !counts) return VLR_ERR_NULL;
+  if (dtype != VLR_F16 && dtype != VLR_BF16) return VLR_ERR_DTYPE;
+  if (T < 0 || T > 0x7fffffff || cells_b <= 0 || slot_b < 0) return VLR_ERR_RANGE;
+  if (h_in < 64 || h_out < 64 || h_in >= 65536 || h_out >= 65536 || (h_in & 63) || (h_out & 63)) return VLR_ERR_SHAPE;
+  if (v_pitch < 8 || v_pitch > kMaxRank || (v_pitch & 7)) return VLR_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(y) || !aligned16(w_base) || !aligned16(v) || !aligned16(wb_pool)) return VLR_ERR_ALIGN;
+  static bool attr_done_dev[64];
+  int cur_dev = 0;
+  if (cudaGetDevice(&cur_dev) != cudaSuccess || cur_dev < 0 || cur_dev >= 64) return VLR_ERR_RANGE;
+  if (!attr_done_dev[cur_dev]) {
+    cudaError_t e = cudaFuncSetAttribute((const void*)fused_proj_kernel<__half>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kFpSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute((const void*)fused_proj_kernel<__nv_bfloat16>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, kFpSmem);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return (int)e;
+    }
+    attr_done_dev[cur_dev] = true;
+  }
+  if (max_mma_tiles <= 0 || max_mma_tiles > T) max_mma_tiles = T;
+  FusedArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  fa.v = v;
+  fa.v_pitch = (int)v_pitch;
+  fa.h_in = (int)h_in;
+  fa.h_out = (int)h_out;
+  int rc;
+  for (int i = 0; i < 3; ++i)                          // X [T, h_in]: boxes of 32 / 64 / 128 rows
+    if ((rc = make_map_2d(&fa.xw.act[i], x, dtype, T, h_in, 32 << i)) != VLR_OK) return rc;
+  // W [h_in, h_out]: boxes of 64 rows (K) x 64 columns (N)
+  if ((rc = make_map_2d(&fa.xw.w[2], w_base, dtype, h_in, h_out, 64)) != VLR_OK) return rc;
+  for (int i = 0; i < 4; ++i)                          // B-side pool [cells, h_out]: 16 .. 128 rows
+    if ((rc = make_map_2d(&fa.yb.w[i], wb_pool, dtype, cells_b, h_out, 16 << i)) != VLR_OK) return rc;
+  TileSource src{};
+  src.mode = 1;
+  src.tiles = tiles;
+  src.counts = counts;
+  src.gather_mma = 0;                                  // consecutive-row tiles only
+  src.a_start = a_start_b;
+  src.a_loc = a_loc_b;
+  src.slot = slot_b;
+  src.status = dev_status;
+  src.max_rank = kMaxRank;
+  src.n_problems = 1;
+  src.nsplit = (int)((h_out + kFpTileN - 1) / kFpTileN);
+  src.max_tiles = max_mma_tiles;
+  const int64_t items = max_mma_tiles * src.nsplit;
+  const unsigned grid = (unsigned)(items < sm_count() ? items : sm_count());
+  if (dtype == VLR_F16)
+    fused_proj_kernel<__half><<<grid, kExpThreads, kFpSmem, (cudaStream_t)stream>>>(fa, (__half*)y, src);
+  else
+    fused_proj_kernel<__nv_bfloat16><<<grid, kExpThreads, kFpSmem, (cudaStream_t)stream>>>(fa, (__nv_bfloat16*)y, src);
+  return launch_status();
 }
 
 extern "C" int vlr_set_tile_table(const vlr_tile_choice_t* entries, int n) {

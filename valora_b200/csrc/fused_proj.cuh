@@ -196,7 +196,6 @@ fused_proj_kernel(const __grid_constant__ FusedArgs fa, T* __restrict__ y, TileS
     // ------------------------------------------------------------ V' staging + epilogue
     const int q = warp & 3;                            // tensor-memory lane quarter = rows 32 q ..
     const int hh = warp >> 2;                          // which 128 of the tile's 256 columns
-    const int row = q * 32 + lane;
     const int et = threadIdx.x;                        // 0..255
     const uint32_t mine = out0 + warp * (32 * 128);    // this warp's staging tile: 32 rows x 64 columns
     uint32_t li = 0;

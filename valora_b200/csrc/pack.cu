@@ -329,9 +329,9 @@ static int pack_check(const int64_t* tok_adapter, int64_t T, const int64_t* a_le
   if (T > 0 && !tok_adapter) return VLR_ERR_NULL;
   if (T < 0 || T > (1 << 24) || n_adapters <= 0 || n_adapters > kPackMaxAdapters || o.tiles_cap < 0)
     return VLR_ERR_RANGE;
-  // a tile is at most one 128-row MMA tile, or 16 gathered rows
+  // a tile is at most one 128-row MMA tile, or 32 gathered rows
   if (tile_m <= 0 || tile_m > 128 || mma_min_rows <= 0 || gather_rows_per_tile <= 0 ||
-      gather_rows_per_tile > 16)
+      gather_rows_per_tile > 32)
     return VLR_ERR_RANGE;
   return VLR_OK;
 }

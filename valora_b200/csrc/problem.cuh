@@ -92,6 +92,9 @@ struct TileSource {
   int64_t trace_cap;
   // device status word of this launch (see raise_status); null = the process-wide one
   int* status;
+  // shrink only: per-adapter scales (launch dtype) applied in fp32 before the single rounding
+  // of the result, for callers that consume a pre-scaled V' (the fused projection); null = none
+  const void* shrink_scales;
   // work distribution: null = item k of a CTA is blockIdx.x + k * gridDim.x; else a
   // zeroed device counter from which the CTAs draw their next item (after the first)
   unsigned int* item_counter;

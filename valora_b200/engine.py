@@ -56,8 +56,8 @@ class LoraStepEngine:
             gather_rows_per_tile = int(self.table["gather_rows_per_tile"]) if gather_path == "mma" else 8
         if gather_path == "simt" and gather_rows_per_tile > 8:
             raise ValueError("the SIMT gather kernels take at most 8 rows per tile")
-        if gather_path == "mma" and gather_rows_per_tile > 16:
-            raise ValueError("a gather tile on the tensor-core path holds at most 16 rows")
+        if gather_path == "mma" and gather_rows_per_tile > 32:
+            raise ValueError("a gather tile on the tensor-core path holds at most 32 rows")
         self.projections = list(projections)
         self.input_of = list(range(len(self.projections))) if input_of is None else [int(i) for i in input_of]
         if len(self.input_of) != len(self.projections):

@@ -217,7 +217,7 @@ def bench_atmm(layers: int, reps: int, warmup: int, dev, eager: bool = False):
     }
 
 
-def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: bool = False):
+def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: bool = False, gather_rows: int = 0):
     """A config through LoraStepEngine.step (device packer + one shrink and one
     expand launch): `layers` copies of the config's projections, every copy with its
     own pools and activations, CUDA events around each stage.  shared_x: q/k/v and
@@ -230,7 +230,8 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
         if len(b.projections) != len(workloads.SHARED_INPUT_OF):
             raise SystemExit("--shared-x needs a config with the seven projections (2 or 3)")
         input_of = list(workloads.SHARED_INPUT_OF)
-    eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T, input_of=input_of)
+    eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T, input_of=input_of,
+                         gather_rows_per_tile=gather_rows or None)
     eng.randomize_weights(seed=b.seed)
     g = torch.Generator(device=dev)
     g.manual_seed(b.seed + 7919)          # another stream than the weights'
@@ -268,6 +269,77 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
         "tokens_per_s": b.T / (step_ms * 1e-3), "algorithmic_bytes": nbytes,
         "gbs": nbytes / (step_ms * 1e-3) / 1e9, "frac": nbytes / (step_ms * 1e-3) / 1e9 / peak,
         "tflops": flops / (step_ms * 1e-3) / 1e12, "peak_gbs": peak, "peak_source": src,
+    }
+
+
+def bench_fused(reps: int, warmup: int, dev, copies: int = 4):
+    """The base projection with the expand folded in (vlr_fused_proj) on the prefill batch of
+    config 2, one 4096 -> 4096 projection, bf16: shrink with the scale applied + the fused
+    kernel, against the unfused sequence torch.mm + shrink + expand on the same tensors.
+    `copies` independent sets of activations are walked per measurement (the base weight
+    and the pools are shared: they are what a layer re-reads)."""
+    b = workloads.config2()
+    dtype = torch.bfloat16
+    H, T, n_ad = workloads.H, b.T, b.n_adapters
+    ranks = [int(r) for r in b.ranks]
+    g = torch.Generator(device=dev)
+    g.manual_seed(2)
+    pa = AdapterPool(sum(ranks) + 16, H, 1, dtype, dev, 1)
+    pb = AdapterPool(sum(ranks) + 16, H, 1, dtype, dev, 1)
+    for pool in (pa, pb):
+        for a in range(n_ad):
+            pool.load_adapter(f"a{a}", ranks[a], workloads.ALPHA / ranks[a], [[None]])
+        pool.buffer[0].copy_((torch.randn(pool.buffer[0].shape, generator=g, device=dev) * 0.02).to(dtype))
+    W = (torch.randn(H, H, generator=g, device=dev) * 0.02).to(dtype)
+    x = [torch.randn(T, H, generator=g, device=dev).to(dtype) for _ in range(copies)]
+    y = [torch.empty(T, H, dtype=dtype, device=dev) for _ in range(copies)]
+    v = [torch.zeros(T, 128, dtype=dtype, device=dev) for _ in range(copies)]
+    idx = torch.from_numpy(b.tok_adapter.astype(np.int64)).to(dev)
+    packer = ops.Packer(T, n_ad, dev)
+    pk0 = packer.pack(idx, pa.a_len, sort=False)
+    P = pk0.host_counts()["P"]
+    tables = tuple(t.clone() for t in (pk0.seg_len, pk0.seg_rank, pk0.seg_adapter, pk0.seg_start))
+    pk = packer.pack(idx, pa.a_len, sort=True)
+    wa = pa.buffer[0].view(pa.buffer[0].shape[0], 32, H // 32)
+    wb = pb.buffer[0].view(pb.buffer[0].shape[0], 32, H // 32)
+    sc = pa.a_scaling
+
+    def shrink(l, scaled):
+        ops.atmm(v[l], x[l], wa, pa.a_start, pa.a_len, pa.a_loc, idx, 0, sc, *tables, None, P, apply_scale=scaled)
+
+    def fused(l):
+        ops.fused_proj(y[l], x[l], W, v[l], pb.buffer[0], pb.a_start, pb.a_loc, 0, pk)
+
+    def unfused(l):
+        torch.mm(x[l], W, out=y[l])
+        shrink(l, False)
+        ops.atmm(y[l], v[l], wb, pb.a_start, pb.a_len, pb.a_loc, idx, 0, sc, *tables, None, P, apply_scale=True)
+
+    ms_f = _time_walk(fused, copies, reps, warmup) / copies
+    ms_sf = _time_walk(lambda l: (shrink(l, True), fused(l)), copies, reps, warmup) / copies
+    ms_mm = _time_walk(lambda l: torch.mm(x[l], W, out=y[l]), copies, reps, warmup) / copies
+    ms_u = _time_walk(unfused, copies, reps, warmup) / copies
+    if ops.device_status() != 0:
+        raise SystemExit("a kernel reported a status")
+    lr = int(b.ranks[b.tok_adapter].astype(np.int64).sum())
+    flops_base, flops_exp = 2.0 * T * H * H, 2.0 * lr * H
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+            peaks = {"bf16_tflops_burst": m.get("bf16_tflops"), "bf16_tflops_sustained": m.get("bf16_tflops_sustained")}
+    except Exception:
+        peaks = {"bf16_tflops_burst": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    tf = (flops_base + flops_exp) / (ms_f * 1e-3) / 1e12
+    return {
+        "bench": "fused_base_projection", "workload": b.name + " (q projection, bf16)", "tokens": T, "hidden": H,
+        "ranks": sorted(set(ranks)), "mma_tiles": pk.host_counts()["n_mma"], "copies_walked": copies,
+        "fused_kernel_ms": ms_f, "fused_kernel_tflops": tf,
+        "frac_of_sustained_peak": tf / peaks["bf16_tflops_sustained"] if peaks.get("bf16_tflops_sustained") else None,
+        "shrink_plus_fused_ms": ms_sf, "unfused_mm_shrink_expand_ms": ms_u, "torch_mm_alone_ms": ms_mm,
+        "torch_mm_tflops": flops_base / (ms_mm * 1e-3) / 1e12,
+        "hbm_bytes_fused": (2 * T * H + H * H) * 2, "hbm_bytes_unfused": (2 * T * H + H * H + 3 * T * H) * 2,
+        "peaks": peaks,
     }
 
 
@@ -337,6 +409,9 @@ def main():
                     help="config 1 only: the 9-argument decode call (default) or the step API")
     ap.add_argument("--shared-x", action="store_true",
                     help="step API, configs 2 and 3: q/k/v and up/gate read one X per copy")
+    ap.add_argument("--fused", action="store_true",
+                    help="the base projection with the expand folded in, on config 2's q projection")
+    ap.add_argument("--gather-rows", type=int, default=0, help="step API: rows per gather tile (default: the table's)")
     ap.add_argument("--trace", choices=["shrink", "expand"],
                     help="step API: print the stage timing of CTA 0 of one launch instead of timing steps")
     args = ap.parse_args()
@@ -344,7 +419,9 @@ def main():
         raise SystemExit("microbench needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    if args.trace:
+    if args.fused:
+        print(json.dumps(bench_fused(args.reps, args.warmup, dev)))
+    elif args.trace:
         default_layers = {0: 1, 1: 4, 2: 2, 3: 4, 4: 2}[args.config]
         print(json.dumps(trace_step(args.config, args.layers or default_layers, args.trace, dev)))
     elif args.config == 0:
@@ -354,7 +431,7 @@ def main():
     else:
         default_layers = {1: 32, 2: 4, 3: 32, 4: 8}[args.config]
         print(json.dumps(bench_step(args.config, args.layers or default_layers, args.reps, args.warmup, dev,
-                                    args.shared_x)))
+                                    args.shared_x, args.gather_rows)))
 
 
 if __name__ == "__main__":

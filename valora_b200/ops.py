@@ -150,6 +150,8 @@ def atmm(y, x, w, start_indicies, lora_ranks, loc_indicies, indicies, qkvo, lora
              | (ATMM_FULL_TILES if full_tiles else 0))
     if apply_scale:
         _check_input(lora_scales, "lora_scales")
+        if lora_scales.dtype != x.dtype:
+            raise RuntimeError("lora_scales must have the dtype of x")
     lib = _bind(x.device)
     with _nvtx("vlr.atmm_shrink" if h_in >= h_out else "vlr.atmm_expand"):
         rc = lib.vlr_atmm(_ptr(y), _ptr(x), _ptr(w), _ptr(start_indicies), _ptr(lora_ranks),
@@ -188,8 +190,8 @@ class Packer:
 
     def __init__(self, max_tokens: int, n_adapters: int, device, tile_m: int = 128,
                  mma_min_rows: int = 16, gather_rows_per_tile: int = 8):
-        if not (0 < tile_m <= 128) or mma_min_rows <= 0 or not (0 < gather_rows_per_tile <= 16):
-            raise RuntimeError("a tile holds at most 128 consecutive rows or 16 gathered rows")
+        if not (0 < tile_m <= 128) or mma_min_rows <= 0 or not (0 < gather_rows_per_tile <= 32):
+            raise RuntimeError("a tile holds at most 128 consecutive rows or 32 gathered rows")
         self.lib = _bind(torch.device(device))
         self.device = torch.device(device)
         self.max_tokens, self.n_adapters = int(max_tokens), int(n_adapters)
@@ -261,6 +263,37 @@ def pack_static(packer: "Packer", tok_adapter: torch.Tensor, a_len: torch.Tensor
     _lib.check(rc, "vlr_pack_static")
     return Packed(T, packer.perm, packer.seg_len, packer.seg_rank, packer.seg_adapter,
                   packer.seg_start, packer.tiles, packer.gather_rows, packer.counts, None)
+
+
+def fused_proj(y: torch.Tensor, x: torch.Tensor, w_base: torch.Tensor, v: torch.Tensor, wb_pool: torch.Tensor,
+               a_start_b: torch.Tensor, a_loc_b: torch.Tensor, slot_b: int, packed: Packed,
+               status: Optional[torch.Tensor] = None):
+    """y[rows] = x[rows] @ w_base + v[rows, :r] @ B_adapter for the rows of the packed batch's
+    consecutive-row tiles: the base projection (torch.mm in the reference,
+    lora_unordered_batch_infer.py:885 / :1568) with the LoRA expand as extra steps of the same
+    K loop, so y is written once and never read.  v is the shrink result with the adapter
+    scale already applied (atmm(..., apply_scale=True) on the shrink).  Rows in gather tiles
+    are left alone."""
+    for t, n in ((y, "y"), (x, "x"), (w_base, "w_base"), (v, "v"), (wb_pool, "wb_pool")):
+        _check_input(t, n)
+        if t.dtype != x.dtype:
+            raise RuntimeError("y, x, w_base, v and wb_pool must share one dtype")
+    for t, n in ((a_start_b, "a_start_b"), (a_loc_b, "a_loc_b")):
+        _check_input(t, n)
+        _i64(t, n)
+    T, h_in = x.shape
+    h_out = y.size(1)
+    if w_base.shape != (h_in, h_out) or y.size(0) != T or v.size(0) != T or packed.T != T:
+        raise RuntimeError("shape mismatch between x, w_base, y, v and the packed batch")
+    if wb_pool.numel() % h_out:
+        raise RuntimeError("pool size is not a multiple of the row width")
+    lib = _bind(x.device)
+    with _nvtx("vlr.fused_proj"):
+        rc = lib.vlr_fused_proj(_ptr(y), _ptr(x), _ptr(w_base), _ptr(v), v.size(1), _ptr(wb_pool),
+                                wb_pool.numel() // h_out, _ptr(a_start_b), _ptr(a_loc_b), int(slot_b),
+                                _ptr(packed.tiles), _ptr(packed.counts), 0, T, h_in, h_out, _dtype_code(x),
+                                _ptr(status), _stream(x.device))
+    _lib.check(rc, "vlr_fused_proj")
 
 
 def var_len_copy(old_a_start, old_a_len, old_a_location, new_a_start, new_a_location):

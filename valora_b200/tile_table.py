@@ -32,7 +32,7 @@ BUILTIN = {
         {"max_rank": 64, "step": 0, "shrink_stages": 4, "expand_stages": 4, "small_call_rows": 32},
         {"max_rank": 128, "step": 0, "shrink_stages": 3, "expand_stages": 3, "small_call_rows": 32},
     ],
-    "engine": {"mma_min_rows": 16, "gather_rows_per_tile": 16, "wide_gather_below_rank": 33},
+    "engine": {"mma_min_rows": 16, "gather_rows_per_tile": 32, "wide_gather_below_rank": 33},
 }
 
 
