@@ -578,13 +578,13 @@ def main():
                    "step_frac_of_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
                    "tflops": batch.algorithmic_flops() / (ms_per_step * 1e-3) / 1e12,
                    "phase_ms": phase_ms, "phase_algorithmic_bytes": pbytes,
-                   "launches_per_step": "packer (5 small kernels) + 1 memset + shrink + expand: one call, "
+                   "launches_per_step": "packer (4 small kernels) + 1 memset + shrink + expand: one call, "
                                         "two launches that cover all problems",
                    "per_rank": per_rank},
         "parity": parity,
         "clocks": clocks,
         "e2e": e2e,
-        "gpu_launches": (5 + len(kernel_names)) * K,
+        "gpu_launches": (4 + len(kernel_names)) * K,
         "roofline": {"kernel": dom, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                      "algorithmic_bytes_per_launch": pbytes[dom], "ms_per_launch": phase_ms[dom]},

@@ -272,7 +272,7 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
     }
 
 
-def bench_fused(reps: int, warmup: int, dev, copies: int = 4):
+def bench_fused(reps: int, warmup: int, dev, copies: int = 4, eager: bool = False):
     """The base projection with the expand folded in (vlr_fused_proj) on the prefill batch of
     config 2, one 4096 -> 4096 projection, bf16: shrink with the scale applied + the fused
     kernel, against the unfused sequence torch.mm + shrink + expand on the same tensors.
@@ -315,10 +315,10 @@ def bench_fused(reps: int, warmup: int, dev, copies: int = 4):
         shrink(l, False)
         ops.atmm(y[l], v[l], wb, pb.a_start, pb.a_len, pb.a_loc, idx, 0, sc, *tables, None, P, apply_scale=True)
 
-    ms_f = _time_walk(fused, copies, reps, warmup) / copies
-    ms_sf = _time_walk(lambda l: (shrink(l, True), fused(l)), copies, reps, warmup) / copies
-    ms_mm = _time_walk(lambda l: torch.mm(x[l], W, out=y[l]), copies, reps, warmup) / copies
-    ms_u = _time_walk(unfused, copies, reps, warmup) / copies
+    ms_f = _time_walk(fused, copies, reps, warmup, eager) / copies
+    ms_sf = _time_walk(lambda l: (shrink(l, True), fused(l)), copies, reps, warmup, eager) / copies
+    ms_mm = _time_walk(lambda l: torch.mm(x[l], W, out=y[l]), copies, reps, warmup, eager) / copies
+    ms_u = _time_walk(unfused, copies, reps, warmup, eager) / copies
     if ops.device_status() != 0:
         raise SystemExit("a kernel reported a status")
     lr = int(b.ranks[b.tok_adapter].astype(np.int64).sum())
@@ -420,7 +420,7 @@ def main():
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     if args.fused:
-        print(json.dumps(bench_fused(args.reps, args.warmup, dev)))
+        print(json.dumps(bench_fused(args.reps, args.warmup, dev, eager=args.eager)))
     elif args.trace:
         default_layers = {0: 1, 1: 4, 2: 2, 3: 4, 4: 2}[args.config]
         print(json.dumps(trace_step(args.config, args.layers or default_layers, args.trace, dev)))
