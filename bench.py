@@ -317,15 +317,9 @@ def config4_block(dist, dev, rank, world, steps, warmup, peak):
     for name, hot in runs:
         if hot is None:
             s = shard.route(g.req_adapter, g.req_len, world, rank)
-            own = shard.owned_adapters(g.n_adapters, world, rank)
-            ranks = g.ranks[own]
         else:
             s = shard.route_with_replication(g.req_adapter, g.req_len, world, rank, hot, g.n_adapters)
-            base = shard.replicated_base(g.n_adapters, world)
-            ranks = np.full(base + len(hot), 16, np.int64)          # ids no adapter maps to keep a small dummy
-            own = shard.owned_adapters(g.n_adapters, world, rank)
-            ranks[:len(own)] = g.ranks[own]
-            ranks[base:] = g.ranks[hot]
+        ranks = shard.local_ranks(g.ranks, world, rank, hot)
         T = s.T
         rec = {"T": T, "ms": None}
         if T > 0:

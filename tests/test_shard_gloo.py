@@ -183,4 +183,12 @@ def test_replicating_hot_adapters_evens_the_load():
             assert np.array_equal(hot[s.tok_adapter[glob_hot] - base], b.tok_adapter[s.tok_index][glob_hot])
             part = ~glob_hot
             assert np.array_equal(shard.global_id(s.tok_adapter[part], world, s.rank), b.tok_adapter[s.tok_index][part])
+            # the pools' rank table in local numbering matches every token's true adapter rank
+            lr = shard.local_ranks(b.ranks, world, s.rank, hot)
+            assert np.array_equal(lr[s.tok_adapter], b.ranks[b.tok_adapter[s.tok_index]])
+        for r, s in enumerate(plain):
+            lr = shard.local_ranks(b.ranks, world, r)
+            assert np.array_equal(lr[s.tok_adapter], b.ranks[b.tok_adapter[s.tok_index]])
+    odd = shard.local_ranks(np.array([8, 16, 32, 64, 128]), 2, 1, np.array([0]))      # GPU 1 owns 2 of 5
+    assert list(odd) == [16, 64, 16, 8]
     assert len(shard.pick_replicated(counts, 0)) == 0

@@ -2,7 +2,8 @@
 // segments, exclusive-scan offsets and the tile schedule.  Integer work only;
 // every output is a pure function of the inputs (no atomics decide an order).
 //
-// Four small launches on one stream (nothing has to be cleared ahead of them):
+// Batches of up to 1024 rows: ONE launch (pack_tiles sorts in shared memory first).  Larger
+// ones: four small launches on one stream (nothing has to be cleared ahead of them):
 //   1. pack_hist     per-block adapter histograms (blocks of kPackBlock tokens)
 //   2. pack_scan     per-adapter exclusive prefix over blocks + adapter bases
 //   3. pack_scatter  stable placement: perm and the sorted key array
@@ -17,6 +18,10 @@ namespace vlr {
 constexpr int kPackBlock = 256;      // tokens per histogram block
 constexpr int kPackMaxAdapters = 8192;
 constexpr int kScanThreads = 1024;
+constexpr int kPackFusedBits = 13;                     // row index bits of a sort key
+constexpr int kPackFusedTokens = 1024;                 // batches up to this size are packed by ONE launch
+static_assert(kPackFusedTokens <= (1 << kPackFusedBits) && kPackMaxAdapters <= (1 << (32 - kPackFusedBits - 1)),
+              "adapter id and row index must fit one 32-bit sort key below the padding value");
 
 struct PackWs {
   int32_t* hist;        // [nblk][n_adapters]
@@ -167,6 +172,7 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
   __shared__ int warp_sums[33];
   __shared__ int s_P, s_C;
   const int tid = threadIdx.x;
+  extern __shared__ uint32_t sort_keys[];              // sorted == 2 only: the batch's (adapter, row) keys
 
   // every count is written by this kernel (nothing has to be cleared ahead of it); the
   // status starts from the ids themselves
@@ -180,6 +186,38 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     }
   }
   bad = __syncthreads_or(bad);
+  if (sorted == 2) {
+    // Batches of up to kPackFusedTokens rows (decode steps) are sorted right here instead of by
+    // the three launches ahead of this one - larger ones are not: at 4096 rows this sort alone
+    // takes longer than those launches.  A bitonic sort in shared memory of (adapter << 13 | row),
+    // which orders by adapter and keeps the batch order inside an adapter - the same
+    // permutation as the stable counting sort, bit for bit.
+    int n2 = 32;
+    while (n2 < T) n2 <<= 1;
+    for (int i = tid; i < n2; i += kScanThreads)
+      sort_keys[i] = i < T ? ((uint32_t)clamp_id(tok[i], n_adapters) << kPackFusedBits) | (uint32_t)i : 0xffffffffu;
+    __syncthreads();
+    for (int k = 2; k <= n2; k <<= 1) {
+      for (int j = k >> 1; j > 0; j >>= 1) {
+        for (int i = tid; i < n2; i += kScanThreads) {
+          const int p = i ^ j;
+          if (p > i) {
+            const uint32_t a = sort_keys[i], b = sort_keys[p];
+            if ((a > b) == ((i & k) == 0)) {
+              sort_keys[i] = b;
+              sort_keys[p] = a;
+            }
+          }
+        }
+        __syncthreads();
+      }
+    }
+    for (int i = tid; i < T; i += kScanThreads) {
+      out.perm[i] = (int32_t)(sort_keys[i] & ((1u << kPackFusedBits) - 1u));
+      ws.key[i] = (int32_t)(sort_keys[i] >> kPackFusedBits);
+    }
+    __syncthreads();
+  }
   const int32_t* key = ws.key;
   const int32_t* row = out.perm;
 
@@ -307,6 +345,14 @@ static int pack_launch(const int64_t* tok_adapter, int64_t T, const int64_t* a_l
                        int sort, int tile_m, int mma_min_rows, int gather_rows_per_tile,
                        const PackWs& ws, const PackOut& out, cudaStream_t s) {
   const int nblk = (int)((T + kPackBlock - 1) / kPackBlock);
+  if (sort && T > 0 && T <= kPackFusedTokens) {
+    int n2 = 32;
+    while (n2 < T) n2 <<= 1;
+    pack_tiles_kernel<<<1, kScanThreads, n2 * sizeof(uint32_t), s>>>(tok_adapter, a_len, (int)T, (int)n_adapters, 2,
+                                                                     tile_m, mma_min_rows, gather_rows_per_tile,
+                                                                     ws, out);
+    return launch_status();
+  }
   if (sort && T > 0) {
     pack_hist_kernel<<<nblk, kPackBlock, n_adapters * sizeof(int32_t), s>>>(
         tok_adapter, (int)T, (int)n_adapters, ws.hist);

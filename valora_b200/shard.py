@@ -168,6 +168,25 @@ def route_with_replication(req_adapter: np.ndarray, req_len: np.ndarray, world: 
     return Shard(rank, world, keep.astype(np.int64), loc, lens, tok_index, np.repeat(loc, lens).astype(np.int32))
 
 
+def local_ranks(adapter_ranks: np.ndarray, world: int, rank: int, replicated: Optional[np.ndarray] = None,
+                filler: int = 16) -> np.ndarray:
+    """Rank of every LOCAL adapter id of GPU `rank`'s pools: its partitioned adapters at
+    a // world, then (with `replicated`) the replicated ones from replicated_base() on, in
+    ascending global id - the numbering route() / route_with_replication() use.  Local ids
+    no adapter maps to (a GPU that owns one adapter fewer than the others) get `filler`."""
+    adapter_ranks = np.asarray(adapter_ranks, np.int64)
+    n = adapter_ranks.shape[0]
+    own = owned_adapters(n, world, rank)
+    if replicated is None:
+        return adapter_ranks[own].copy()
+    replicated = np.sort(np.asarray(replicated, np.int64))
+    base = replicated_base(n, world)
+    out = np.full(base + replicated.shape[0], int(filler), np.int64)
+    out[:own.shape[0]] = adapter_ranks[own]
+    out[base:] = adapter_ranks[replicated]
+    return out
+
+
 def replicated_base(n_adapters: int, world: int) -> int:
     """First local id used for replicated adapters: one past the largest partitioned local id."""
     return (int(n_adapters) + int(world) - 1) // int(world)
