@@ -226,7 +226,7 @@ typedef struct {
   int32_t shrink_stages;   /* 2, 3 or 4 stages of 96 / 64 / 48 KB; ranks above 64 need <= 3 */
   int32_t expand_stages;   /* 3 or 4 stages of 64 / 48 KB; ranks above 64 need 3 */
   int32_t small_call_rows; /* vlr_atmm shrink with T/128 + num_problems <= half the SMs: 32, 64 or 128 */
-  int32_t reserved;        /* 0 */
+  int32_t wide_gather_below_rank; /* expand: gather tiles of adapters below this rank use wide stages (0: none) */
 } vlr_tile_choice_t;
 int vlr_set_tile_table(const vlr_tile_choice_t* entries, int n);   /* n <= 16; n = 0: built-in rules */
 int vlr_get_tile_choice(int step, int max_rank, vlr_tile_choice_t* out);
@@ -320,12 +320,18 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
  * two SIMT gather launches are skipped.  gather_rows_per_tile must be <= 32 with
  * this flag and <= 8 without it.  Plans need h_in and h_out multiples of 64. */
 #define VLR_STEP_GATHER_ON_TENSOR_CORES 16
-/* or-ed into phase_mask together with VLR_STEP_GATHER_ON_TENSOR_CORES: a gather
- * stage of the expand carries as many 64-column blocks as the stage holds (up to
- * 1024 columns) instead of at most four.  Pays when the batch has adapters of
- * rank 32 or less (their weight rows fill a fraction of a stage otherwise); at
- * rank 64 the plain form is the faster one. */
+/* or-ed into phase_mask together with VLR_STEP_GATHER_ON_TENSOR_CORES.  A gather
+ * stage of the expand carries four 64-column blocks (two above rank 64), or - the
+ * wide form - as many as the stage holds (up to 1024 columns), which pays for
+ * small ranks whose weight rows fill a fraction of a stage otherwise.
+ * VLR_STEP_WIDE_GATHER_STAGES: adapters of small rank may be in the batch; the form
+ * is then chosen per tile, wide for adapters below the tile table's
+ * wide_gather_below_rank.  Without it every gather tile takes the plain form (and
+ * the kernel that runs has no per-tile choice to make, which the consecutive-row
+ * tiles of the same launch gain from).  VLR_STEP_ALL_WIDE_GATHER_STAGES, with the
+ * first: every gather tile takes the wide form (measurements, tests). */
 #define VLR_STEP_WIDE_GATHER_STAGES 32
+#define VLR_STEP_ALL_WIDE_GATHER_STAGES 64
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
                   const int32_t* counts, const void* scales, int max_h_in, int max_h_out,

@@ -49,6 +49,16 @@ def test_host_validation_codes_without_a_gpu():
     assert lib.vlr_pack_static(one, 9000, one, 8, 1, 128, 16, 8, one, one, one, one, one, one, 10, one, one,
                                null) == -9                                                      # beyond the built-in scratch
     assert lib.vlr_selftest_bounded_wait(0, null, null, null) == -6
+    # fused base projection: y, x, w_base, v, v_pitch, wb_pool, cells_b, a_start_b, a_loc_b, slot_b, tiles,
+    # counts, max_mma_tiles, T, h_in, h_out, dtype, dev_status, stream
+    assert lib.vlr_fused_proj(one, one, null, one, 64, one, 8, one, one, 0, one, one, 0, 10, 4096, 4096, 1,
+                              null, null) == -1                                                 # no base weight
+    assert lib.vlr_fused_proj(one, one, one, one, 64, one, 8, one, one, 0, one, one, 0, 10, 4096, 4100, 1,
+                              null, null) == -2                                                 # width % 64
+    assert lib.vlr_fused_proj(one, one, one, one, 60, one, 8, one, one, 0, one, one, 0, 10, 4096, 4096, 1,
+                              null, null) == -2                                                 # rank buffer pitch % 8
+    assert lib.vlr_fused_proj(one, one, one, one, 64, one, 8, one, one, 0, one, one, 0, 0, 4096, 4096, 1,
+                              null, null) == 0                                                  # empty batch
     assert b"workspace" in lib.vlr_error_string(-5)
 
 
@@ -127,8 +137,8 @@ def test_launcher_follows_the_tile_table():
     tile_table.apply(lib, t)
     for e in t["entries"]:
         got = tile_table.choice(lib, bool(e["step"]), e["max_rank"])
-        assert {k: got[k] for k in ("shrink_stages", "expand_stages", "small_call_rows")} == \
-            {k: e[k] for k in ("shrink_stages", "expand_stages", "small_call_rows")}, e
+        keys = ("shrink_stages", "expand_stages", "small_call_rows", "wide_gather_below_rank")
+        assert {k: got[k] for k in keys} == {k: e[k] for k in keys}, e
     by = {(e["step"], e["max_rank"]): e for e in t["entries"]}
     assert tile_table.choice(lib, True, 16)["shrink_stages"] == by[(1, 64)]["shrink_stages"]
     assert tile_table.choice(lib, True, 96)["shrink_stages"] == by[(1, 128)]["shrink_stages"]

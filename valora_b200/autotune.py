@@ -15,9 +15,9 @@ What is swept (one B200, CUDA events, medians over --reps steps after warm-up):
   tiles a shrink with few rows is cut into (32 / 64 / 128);
 * engine thresholds: the run length from which consecutive rows go to 128-row
   tiles instead of gather tiles (8 / 16 / 32) and the smallest resident rank
-  below which the expand uses its wide gather stages (never / < 17 / < 33 / < 65),
-  on the decode-heavy batch with all adapters at rank 16, 32 and 64 and with the
-  mixed ranks.
+  below which a gather tile of the expand uses the wide stage form (decided per
+  tile; never / < 17 / < 33 / < 65 / all), on the decode-heavy batch with all
+  adapters at rank 16, 32, 64 and 128; and the rows per gather tile (16 / 32).
 
 The reference's counterpart is the table shape_to_config in
 valora/models/peft/lora_unordered_batch_infer.py:25-172 (six CUTLASS tile
@@ -125,8 +125,8 @@ def main():
     torch.cuda.set_device(dev)
     lib = _lib.load()
     base = json.loads(json.dumps(tile_table.BUILTIN))
-    s64 = dict(shrink_stages=4, expand_stages=4, small_call_rows=32)
-    s128 = dict(shrink_stages=3, expand_stages=3, small_call_rows=32)
+    s64 = dict(shrink_stages=4, expand_stages=4, small_call_rows=32, wide_gather_below_rank=33)
+    s128 = dict(shrink_stages=3, expand_stages=3, small_call_rows=32, wide_gather_below_rank=33)
     c64, c128 = dict(s64), dict(s128)
     log = {}
 
@@ -138,21 +138,22 @@ def main():
     # ---- steps, rank <= 64: shrink and expand stages, each by its own kernel time
     res = {}
     for ss, es in ((4, 4), (3, 3), (2, 4)):
-        use(s64=dict(shrink_stages=ss, expand_stages=es, small_call_rows=32))
+        use(s64=dict(shrink_stages=ss, expand_stages=es, small_call_rows=32, wide_gather_below_rank=33))
         res[(ss, es)] = _step_ms(workloads.config3(), L3, args.reps, dev)
     shrink_ms = {4: res[(4, 4)][0], 3: res[(3, 3)][0], 2: res[(2, 4)][0]}
     expand_ms = {4: res[(4, 4)][1], 3: res[(3, 3)][1]}
     s64 = dict(shrink_stages=min(shrink_ms, key=shrink_ms.get), expand_stages=min(expand_ms, key=expand_ms.get),
-               small_call_rows=32)
+               small_call_rows=32, wide_gather_below_rank=33)
     log["step_rank64"] = {"workload": f"cfg3 x {L3} layers", "shrink_ms_by_stages": shrink_ms, "expand_ms_by_stages": expand_ms}
     # ---- steps that may meet rank 128
     shrink_ms = {}
     for ss in (3, 2):
-        use(s128=dict(shrink_stages=ss, expand_stages=3, small_call_rows=32))
+        use(s128=dict(shrink_stages=ss, expand_stages=3, small_call_rows=32, wide_gather_below_rank=33))
         a = _step_ms(workloads.config2(), L2, args.reps, dev)
         b = _step_ms(workloads.config4(), L4, args.reps, dev)
         shrink_ms[ss] = a[0] + b[0]
-    s128 = dict(shrink_stages=min(shrink_ms, key=shrink_ms.get), expand_stages=3, small_call_rows=32)
+    s128 = dict(shrink_stages=min(shrink_ms, key=shrink_ms.get), expand_stages=3, small_call_rows=32,
+                wide_gather_below_rank=33)
     log["step_rank128"] = {"workload": f"cfg2 x {L2} + cfg4 x {L4}", "shrink_ms_by_stages": shrink_ms}
     # ---- single calls
     for name, ranks, stages_s, stages_e in (("call_rank64", [8, 16, 16, 32], (4, 3, 2), (4, 3)),
@@ -160,20 +161,21 @@ def main():
         best_s, best_e, rec = None, None, {}
         for ss in stages_s:
             for rows in (32, 64, 128):
-                ch = dict(shrink_stages=ss, expand_stages=stages_e[0], small_call_rows=rows)
+                ch = dict(shrink_stages=ss, expand_stages=stages_e[0], small_call_rows=rows, wide_gather_below_rank=33)
                 use(**({"c64": ch} if name == "call_rank64" else {"c128": ch}))
                 us = _call_us(ranks, args.reps, dev)[0]
                 rec[f"shrink stages {ss} rows {rows}"] = us
                 if best_s is None or us < best_s[0]:
                     best_s = (us, ss, rows)
         for es in stages_e:
-            ch = dict(shrink_stages=best_s[1], expand_stages=es, small_call_rows=best_s[2])
+            ch = dict(shrink_stages=best_s[1], expand_stages=es, small_call_rows=best_s[2], wide_gather_below_rank=33)
             use(**({"c64": ch} if name == "call_rank64" else {"c128": ch}))
             us = _call_us(ranks, args.reps, dev)[1]
             rec[f"expand stages {es}"] = us
             if best_e is None or us < best_e[0]:
                 best_e = (us, es)
-        ch = dict(shrink_stages=best_s[1], expand_stages=best_e[1], small_call_rows=best_s[2])
+        ch = dict(shrink_stages=best_s[1], expand_stages=best_e[1], small_call_rows=best_s[2],
+                  wide_gather_below_rank=33)
         if name == "call_rank64":
             c64 = ch
         else:
@@ -187,8 +189,10 @@ def main():
         ms = _step_ms(workloads.config4(), L4, args.reps, dev, dict(mma_min_rows=mm))[2] + \
             _step_ms(workloads.config3(), L3, args.reps, dev, dict(mma_min_rows=mm))[2]
         eng_log[f"mma_min_rows {mm}"] = ms
-        if best_ms is None or ms < best_ms:
-            best_min, best_ms = mm, ms
+    best_min, best_ms = 16, eng_log["mma_min_rows 16"]
+    for mm in (8, 32):                                   # another value only if it is clearly (1 %) better
+        if eng_log[f"mma_min_rows {mm}"] < 0.99 * best_ms:
+            best_min, best_ms = mm, eng_log[f"mma_min_rows {mm}"]
     wide = {}
     for r in (16, 32, 64, 128):
         off = _step_ms(_all_ranks(workloads.config4(), r), L4, args.reps, dev, dict(wide_gather=False))[1]
@@ -201,11 +205,19 @@ def main():
         else:
             break
     eng_log["expand_ms_by_rank"] = wide
+    for e in (s64, s128, c64, c128):
+        e["wide_gather_below_rank"] = below
+    rows_ms = {}
+    for gr in (16, 32):
+        rows_ms[gr] = _step_ms(workloads.config4(), L4, args.reps, dev, dict(gather_rows_per_tile=gr))[2] + \
+            _step_ms(workloads.config3(), L3, args.reps, dev, dict(gather_rows_per_tile=gr))[2]
+    best_rows = min(rows_ms, key=rows_ms.get)
+    eng_log["step_ms_by_gather_rows"] = rows_ms
     table = {
         "gpu": torch.cuda.get_device_name(dev),
         "how": "python -m valora_b200.autotune (CUDA events, medians; see the module docstring for what is swept)",
         "entries": _entries(s64, s128, c64, c128),
-        "engine": {"mma_min_rows": best_min, "gather_rows_per_tile": 16, "wide_gather_below_rank": below},
+        "engine": {"mma_min_rows": best_min, "gather_rows_per_tile": best_rows},
         "measurements": {**log, "engine": eng_log},
     }
     with open(args.out, "w") as f:

@@ -734,18 +734,21 @@ constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512 + 512;      // + b
 // bytes in flight per stage.
 struct ExpRange { int nt_begin, nt_count, h_out, ncbt, tile_n; uint32_t bstride, yoff; };
 
-// WIDE: a gather stage takes as many 64-column blocks (weights + 16 Y row pieces each) as
-// it holds - an even number, at most 16 (8 chains of 128 columns x 16 accumulator columns
-// each) - and keeps its Y rows row-major, one copy per row.  For batches with small ranks.
+// Wide gather stages: a gather tile of an adapter below the launch's rank threshold
+// (TileSource::wide_below_rank, from the tile table) takes as many 64-column blocks (weights
+// + the rows' pieces) as the stage holds - an even number, at most 256 / row slots - instead
+// of four: a small rank's weight rows would fill a fraction of a stage otherwise.  Decided
+// per tile, so a pool of mixed ranks gets the better shape for each of its adapters - in the
+// WIDE instantiation only, which a launch uses when such adapters may be in the batch: the
+// other one keeps the stage shape a compile-time matter, and the consecutive-row path of a
+// rank-64 step is 8-18 % faster for it (config 3's expand 5.24 against 6.20 ms).
 template <bool WIDE>
 __device__ __forceinline__ ExpRange exp_range(const TileSource& src, const TileInfo& ti, int h_out) {
   ExpRange r;
   r.h_out = h_out;
   r.bstride = (uint32_t)(((ti.rank + 15) & ~15) * 128);
   r.ncbt = (ti.gather && ti.rank <= 64) ? 4 : 2;
-  if (WIDE && ti.gather) {
-    // as many blocks as the stage holds (weights + the rows' pieces), an even number; a chain of
-    // 128 columns takes as many accumulator columns as the tile has row slots, 128 in all
+  if (WIDE && ti.gather && ti.rank < src.wide_below_rank) {
     const int cap = gather_cap(ti.rows);
     const int n = (int)((uint32_t)src.exp_stage_bytes / (r.bstride + cap * 128)) & ~1;
     const int most = 256 / cap;
@@ -1259,7 +1262,7 @@ static int64_t g_trace_cap = 0;
 // K blocks or column blocks per stage) is derived in the kernels from the stage size.
 constexpr int kMaxTileChoices = 16;
 static vlr_tile_choice_t g_choices[kMaxTileChoices] = {
-    {64, 1, 4, 4, 32, 0}, {128, 1, 3, 3, 32, 0}, {64, 0, 4, 4, 32, 0}, {128, 0, 3, 3, 32, 0}};
+    {64, 1, 4, 4, 32, 33}, {128, 1, 3, 3, 32, 33}, {64, 0, 4, 4, 32, 33}, {128, 0, 3, 3, 32, 33}};
 static int g_n_choices = 4;
 
 static bool choice_ok(const vlr_tile_choice_t& c) {
@@ -1272,7 +1275,7 @@ static bool choice_ok(const vlr_tile_choice_t& c) {
                     kRingBytes / c.expand_stages >= 2 * (kTileM + pad) * 128;
   const bool rows_ok = c.small_call_rows == 32 || c.small_call_rows == 64 || c.small_call_rows == 128;
   return c.max_rank >= 8 && c.max_rank <= kMaxRank && (c.step == 0 || c.step == 1) && stages_ok && fits &&
-         rows_ok;
+         rows_ok && c.wide_gather_below_rank >= 0 && c.wide_gather_below_rank <= kMaxRank + 1;
 }
 
 static const vlr_tile_choice_t* find_choice(int step, int max_rank) {
@@ -1294,6 +1297,11 @@ static void size_rings(TileSource& src, int max_rank, bool step) {
   src.exp_stages = c ? c->expand_stages : (pad <= 64 ? 4 : 3);
   src.shrink_stage_bytes = kRingBytes / src.shrink_stages;
   src.exp_stage_bytes = kRingBytes / src.exp_stages;
+  // wide gather stages (expand): the caller says whether adapters of small rank may be in the
+  // batch (1: the table's threshold decides per tile, -1: every gather tile), else none
+  if (src.wide_below_rank == -1) src.wide_below_rank = kMaxRank + 1;
+  else if (src.wide_below_rank == 1) src.wide_below_rank = c ? c->wide_gather_below_rank : 33;
+  else src.wide_below_rank = 0;
 }
 
 static int small_call_rows(int max_rank) {
@@ -1323,12 +1331,12 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
     set((const void*)atmm_shrink_kernel<__nv_bfloat16, 3>, kShrinkSmem);
     set((const void*)atmm_shrink_kernel<__nv_bfloat16, 4>, kShrinkSmem);
     set((const void*)atmm_expand_kernel<__half, 3, false>, kExpSmem);
-    set((const void*)atmm_expand_kernel<__half, 4, false>, kExpSmem);
-    set((const void*)atmm_expand_kernel<__nv_bfloat16, 3, false>, kExpSmem);
-    set((const void*)atmm_expand_kernel<__nv_bfloat16, 4, false>, kExpSmem);
     set((const void*)atmm_expand_kernel<__half, 3, true>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__half, 4, false>, kExpSmem);
     set((const void*)atmm_expand_kernel<__half, 4, true>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 3, false>, kExpSmem);
     set((const void*)atmm_expand_kernel<__nv_bfloat16, 3, true>, kExpSmem);
+    set((const void*)atmm_expand_kernel<__nv_bfloat16, 4, false>, kExpSmem);
     set((const void*)atmm_expand_kernel<__nv_bfloat16, 4, true>, kExpSmem);
     if (e != cudaSuccess) {
       cudaGetLastError();
@@ -1379,10 +1387,11 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
 #define VLR_EXPAND_LAUNCH(NST, WIDE)                                                  \
   atmm_expand_kernel<T, NST, WIDE><<<grid, kExpThreads, kExpSmem, stream>>>(           \
       maps, (T*)y, (const T*)x, (const T*)scales, src, h_out, h_in, sc)
+    const bool wide = src.wide_below_rank > 0;         // some tile of this launch may take the wide form
     if (src.exp_stages == 4) {
-      if (src.wide_gather) VLR_EXPAND_LAUNCH(4, true); else VLR_EXPAND_LAUNCH(4, false);
+      if (wide) VLR_EXPAND_LAUNCH(4, true); else VLR_EXPAND_LAUNCH(4, false);
     } else {
-      if (src.wide_gather) VLR_EXPAND_LAUNCH(3, true); else VLR_EXPAND_LAUNCH(3, false);
+      if (wide) VLR_EXPAND_LAUNCH(3, true); else VLR_EXPAND_LAUNCH(3, false);
     }
 #undef VLR_EXPAND_LAUNCH
   }
@@ -1538,7 +1547,7 @@ extern "C" int vlr_get_tile_choice(int step, int max_rank, vlr_tile_choice_t* ou
   out->shrink_stages = src.shrink_stages;
   out->expand_stages = src.exp_stages;
   out->small_call_rows = c ? c->small_call_rows : 32;
-  out->reserved = 0;
+  out->wide_gather_below_rank = c ? c->wide_gather_below_rank : 33;
   return VLR_OK;
 }
 

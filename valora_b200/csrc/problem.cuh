@@ -75,7 +75,9 @@ struct TileSource {
   const int32_t* counts;
   const int32_t* gather_rows;
   int gather_mma;                    // 1: gather tiles are work items of the tensor-core kernels too
-  int wide_gather;                   // 1: expand gather stages take as many column blocks as fit (small ranks)
+  int wide_below_rank;               // expand: gather tiles of adapters below this rank use wide stages.  The
+                                     // caller presets 0 (none), 1 (the tile table's threshold) or -1 (all tiles);
+                                     // the launcher resolves it
   // adapter tables
   const int64_t* a_start;
   const int64_t* a_loc;

@@ -81,7 +81,8 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   src.status = dev_status;
   src.max_rank = (max_rank > 0 && max_rank <= kMaxRank) ? max_rank : kMaxRank;
   src.gather_mma = (phase_mask & VLR_STEP_GATHER_ON_TENSOR_CORES) ? 1 : 0;
-  src.wide_gather = (phase_mask & VLR_STEP_WIDE_GATHER_STAGES) ? 1 : 0;
+  src.wide_below_rank = !(phase_mask & VLR_STEP_WIDE_GATHER_STAGES) ? 0
+                        : (phase_mask & VLR_STEP_ALL_WIDE_GATHER_STAGES) ? -1 : 1;
   if (src.gather_mma) {
     // gather tiles are work items of the two tensor-core launches
     max_mma_tiles = T;

@@ -39,8 +39,10 @@ class LoraStepEngine:
         gather_path: "mma" sends rows that are not consecutive in the batch (decode
         tokens) through the tensor-core kernels with gathered rows (up to 128 rows of
         an adapter per tile); "simt" sends them through the gather mat-vec kernels
-        (8 rows per tile).  wide_gather: let a gather stage of the expand take as many
-        columns as fit (default: when an adapter of rank 32 or less is resident).
+        (8 rows per tile).  wide_gather: force the wide (True) or the plain (False) form
+        of the expand's gather stages for every tile; default: when an adapter below the
+        tile table's rank threshold is resident, the form is chosen per tile (wide for
+        those adapters), else plain throughout.
         share_pools_with: another engine over the same projections and adapters whose
         adapter pools this one uses instead of allocating its own (a second view of the
         same resident weights, e.g. with other activation buffers)."""
@@ -99,6 +101,7 @@ class LoraStepEngine:
         self.a_len = any_pool.a_len
         self.scales = any_pool.a_scaling
         self.packer = ops.Packer(self.max_tokens, n_ad, self.device, tile_m, mma_min_rows, gather_rows_per_tile)
+        self._wide_below = int(tile_table.choice(self.packer.lib, True, max(self.ranks))["wide_gather_below_rank"])
         self.x: List[List[torch.Tensor]] = []
         self.y: List[List[torch.Tensor]] = []
         self.plan: Optional[ops.StepPlan] = None
@@ -170,10 +173,12 @@ class LoraStepEngine:
     def _gather_flag(self) -> int:
         if self.gather_path != "mma":
             return 0
-        # adapters of rank 32 or less: let a gather stage of the expand take more columns
-        on = (min(self.ranks) < int(self.table["wide_gather_below_rank"]) if self.wide_gather is None
-              else bool(self.wide_gather))
-        wide = ops.STEP_WIDE_GATHER_STAGES if on else 0
+        # the form of the expand's gather stages: per tile by the tile table's rank threshold when
+        # an adapter below it is resident; forced for every tile when the caller said so
+        if self.wide_gather is None:
+            wide = ops.STEP_WIDE_GATHER_STAGES if min(self.ranks) < self._wide_below else 0
+        else:
+            wide = (ops.STEP_WIDE_GATHER_STAGES | ops.STEP_ALL_WIDE_GATHER_STAGES) if self.wide_gather else 0
         return ops.STEP_GATHER_ON_TENSOR_CORES | wide
 
     def phases(self):

@@ -22,6 +22,7 @@ MAX_RANK = 128
 PHASE_SHRINK_MMA, PHASE_SHRINK_GATHER, PHASE_EXPAND_MMA, PHASE_EXPAND_GATHER, PHASE_ALL = 1, 2, 4, 8, 15
 STEP_GATHER_ON_TENSOR_CORES = 16
 STEP_WIDE_GATHER_STAGES = 32
+STEP_ALL_WIDE_GATHER_STAGES = 64
 
 
 _NVTX = os.environ.get("VLR_NVTX") == "1"

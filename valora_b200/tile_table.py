@@ -8,9 +8,9 @@ get_config_a / get_config_b, :216-236).  Here `tile_table.json` (written by
 `python -m valora_b200.autotune` on the GPU it names) holds, per (step or single
 call, rank bound): how the operand ring is cut into stages for the shrink and
 for the expand, and the row count of a small drop-in shrink's tiles; and for
-the engine: from which consecutive-run length rows go to 128-row tiles instead
-of gather tiles, and below which smallest resident rank the expand's wide
-gather stages are used.  The library gets the launch-level part through
+the expand, below which adapter rank a gather tile uses the wide stage form;
+for the engine: from which consecutive-run length rows go to 128-row tiles
+instead of gather tiles, and how many rows a gather tile takes.  The library gets the launch-level part through
 vlr_set_tile_table when it is loaded; VLR_TILE_TABLE=<path> names another file.
 """
 from __future__ import annotations
@@ -27,18 +27,23 @@ DEFAULT_PATH = os.path.join(HERE, "tile_table.json")
 BUILTIN = {
     "gpu": None,
     "entries": [
-        {"max_rank": 64, "step": 1, "shrink_stages": 4, "expand_stages": 4, "small_call_rows": 32},
-        {"max_rank": 128, "step": 1, "shrink_stages": 3, "expand_stages": 3, "small_call_rows": 32},
-        {"max_rank": 64, "step": 0, "shrink_stages": 4, "expand_stages": 4, "small_call_rows": 32},
-        {"max_rank": 128, "step": 0, "shrink_stages": 3, "expand_stages": 3, "small_call_rows": 32},
+        {"max_rank": 64, "step": 1, "shrink_stages": 4, "expand_stages": 4, "small_call_rows": 32,
+         "wide_gather_below_rank": 33},
+        {"max_rank": 128, "step": 1, "shrink_stages": 3, "expand_stages": 3, "small_call_rows": 32,
+         "wide_gather_below_rank": 33},
+        {"max_rank": 64, "step": 0, "shrink_stages": 4, "expand_stages": 4, "small_call_rows": 32,
+         "wide_gather_below_rank": 33},
+        {"max_rank": 128, "step": 0, "shrink_stages": 3, "expand_stages": 3, "small_call_rows": 32,
+         "wide_gather_below_rank": 33},
     ],
-    "engine": {"mma_min_rows": 16, "gather_rows_per_tile": 32, "wide_gather_below_rank": 33},
+    "engine": {"mma_min_rows": 16, "gather_rows_per_tile": 32},
 }
 
 
 class _Choice(ctypes.Structure):
     _fields_ = [("max_rank", ctypes.c_int32), ("step", ctypes.c_int32), ("shrink_stages", ctypes.c_int32),
-                ("expand_stages", ctypes.c_int32), ("small_call_rows", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+                ("expand_stages", ctypes.c_int32), ("small_call_rows", ctypes.c_int32),
+                ("wide_gather_below_rank", ctypes.c_int32)]
 
 
 _current = None
@@ -71,7 +76,7 @@ def apply(lib, table: Optional[dict] = None) -> dict:
     arr = (_Choice * max(len(ent), 1))()
     for i, e in enumerate(ent):
         arr[i] = _Choice(int(e["max_rank"]), int(e["step"]), int(e["shrink_stages"]), int(e["expand_stages"]),
-                         int(e["small_call_rows"]), 0)
+                         int(e["small_call_rows"]), int(e.get("wide_gather_below_rank", 33)))
     rc = lib.vlr_set_tile_table(ctypes.cast(arr, ctypes.c_void_p), len(ent))
     if rc != 0:
         raise RuntimeError(f"vlr_set_tile_table refused the table (code {rc}): {ent}")
@@ -90,4 +95,5 @@ def choice(lib, step: bool, max_rank: int) -> dict:
     if rc != 0:
         raise RuntimeError(f"vlr_get_tile_choice failed (code {rc})")
     return {"max_rank": c.max_rank, "step": c.step, "shrink_stages": c.shrink_stages,
-            "expand_stages": c.expand_stages, "small_call_rows": c.small_call_rows}
+            "expand_stages": c.expand_stages, "small_call_rows": c.small_call_rows,
+            "wide_gather_below_rank": c.wide_gather_below_rank}
