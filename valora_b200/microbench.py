@@ -217,13 +217,22 @@ def bench_atmm(layers: int, reps: int, warmup: int, dev, eager: bool = False):
     }
 
 
-def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: bool = False, gather_rows: int = 0):
+def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: bool = False, gather_rows: int = 0,
+               model: bool = False, graph: bool = False):
     """A config through LoraStepEngine.step (device packer + one shrink and one
     expand launch): `layers` copies of the config's projections, every copy with its
     own pools and activations, CUDA events around each stage.  shared_x: q/k/v and
-    up/gate of a copy read one X each (configs with the seven projections)."""
+    up/gate of a copy read one X each (configs with the seven projections).
+    model: the config's batch over the seven Qwen-VL-7B-shaped projections of every
+    layer instead of the config's own single projection (a decode step of the whole
+    model for config 1).  graph: the step is also captured into a CUDA graph and the
+    replays are timed (`graph_ms_per_step`): what a serving loop that replays its
+    decode step pays, without the host's launch path between the kernels."""
     from .engine import LoraStepEngine
     b = workloads.CONFIGS[config]()
+    if model:
+        b.projections = list(workloads.PROJECTIONS)
+        b.name += "_7proj"
     b.layers = layers
     input_of = None
     if shared_x:
@@ -260,7 +269,34 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
     peak, src = _peak()
     step_ms = float(np.median(tot))
     nbytes, flops = b.algorithmic_bytes(input_of), b.algorithmic_flops()
-    return {
+    graph_ms = None
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            eng.step(tok)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g_ = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_):
+            eng.step(tok)
+        g_.replay()
+        torch.cuda.synchronize()
+        gt = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g_.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            gt.append(e0.elapsed_time(e1))
+        graph_ms = float(np.median(gt))
+        if ops.device_status() != 0:
+            raise SystemExit("a bounded wait gave up inside a kernel")
+    extra = {} if graph_ms is None else {"graph_ms_per_step": graph_ms,
+                                         "graph_gbs": nbytes / (graph_ms * 1e-3) / 1e9,
+                                         "graph_frac": nbytes / (graph_ms * 1e-3) / 1e9 / peak}
+    return {**extra,
         "bench": "lora_step", "shared_x": bool(shared_x), "workload": b.name, "dtype": str(b.dtype).replace("torch.", ""), "tokens": b.T,
         "adapters": b.n_adapters, "adapters_touched": int(len(b.touched())),
         "ranks": sorted(set(int(r) for r in b.ranks)), "projections": len(b.projections), "layers": layers,
@@ -412,6 +448,9 @@ def main():
     ap.add_argument("--fused", action="store_true",
                     help="the base projection with the expand folded in, on config 2's q projection")
     ap.add_argument("--gather-rows", type=int, default=0, help="step API: rows per gather tile (default: the table's)")
+    ap.add_argument("--model", action="store_true",
+                    help="step API: the batch over the seven model projections per layer instead of the config's own")
+    ap.add_argument("--graph", action="store_true", help="step API: also time replays of the step from a CUDA graph")
     ap.add_argument("--trace", choices=["shrink", "expand"],
                     help="step API: print the stage timing of CTA 0 of one launch instead of timing steps")
     args = ap.parse_args()
@@ -431,7 +470,7 @@ def main():
     else:
         default_layers = {1: 32, 2: 4, 3: 32, 4: 8}[args.config]
         print(json.dumps(bench_step(args.config, args.layers or default_layers, args.reps, args.warmup, dev,
-                                    args.shared_x, args.gather_rows)))
+                                    args.shared_x, args.gather_rows, args.model, args.graph)))
 
 
 if __name__ == "__main__":
