@@ -1011,3 +1011,65 @@ def test_fused_projection_matches_base_plus_lora(ops, dtype):
     assert own_error(y[dev(rows)], same_v[rows]) <= 1e-4            # fp32 accumulation order only
     assert _err(y[dev(rows)], truth[rows]) <= TOL
     assert own_error(y[dev(rows)], truth[rows]) <= OWN_TOL
+
+
+def test_results_do_not_depend_on_the_tile_table(ops):
+    """The tile table changes how a launch is cut into stages and tiles, never what it
+    computes: a drop-in shrink + expand and a step give bit-identical results under every
+    choice the table may hold (ring of 2 / 3 / 4 stages, small-call tiles of 32 / 64 / 128 rows,
+    wide gather stages for no / some / all adapters)."""
+    import json
+    from valora_b200 import _lib, tile_table
+    from valora_b200.engine import LoraStepEngine
+    lib = _lib.load()
+    base = tile_table.load(tile_table.DEFAULT_PATH)
+
+    def table(ss, es, rows, wide):
+        t = json.loads(json.dumps(base))
+        for e in t["entries"]:
+            e.update(shrink_stages=min(ss, 3) if e["max_rank"] > 64 else ss, expand_stages=3 if e["max_rank"] > 64 else es,
+                     small_call_rows=rows, wide_gather_below_rank=wide)
+        return t
+
+    dtype, h = torch.bfloat16, 1024
+    ranks = [16, 64, 8, 32]
+    seg_len, seg_ad = [5, 140, 33, 1, 70], [0, 1, 2, 3, 1]
+    A, B = rand_lora(ranks, h, h, dtype, n_slots=1, seed=61)
+    a_start, a_len, a_loc, total = build_tables(ranks, 1, shuffle=True, contiguous_slots=True, seed=62)
+    wa = fill_pool_a(A, ranks, a_start, a_loc, total, h, dtype).to(DEV)
+    wb = fill_pool_b(B, ranks, a_start, a_loc, total, h, dtype, layout="rows").to(DEV)
+    T = sum(seg_len)
+    g = torch.Generator().manual_seed(63)
+    x = torch.randn(T, h, generator=g).to(dtype).to(DEV)
+    y0 = torch.randn(T, h, generator=g).to(dtype).to(DEV)
+    oc, rc = t64(seg_len, DEV), t64([ranks[a] for a in seg_ad], DEV)
+    li, si = t64(seg_ad, DEV), t64(np.concatenate([[0], np.cumsum(seg_len)]), DEV)
+    idx = torch.zeros(T, dtype=torch.int64, device=DEV)
+    sc = torch.tensor([16.0 / r for r in ranks]).to(dtype).to(DEV)
+    tabs = (t64(a_start, DEV), t64(a_len, DEV), t64(a_loc, DEV))
+    # a step on a decode-heavy batch with small and large ranks (gather tiles of both stage forms)
+    b4 = workloads.config4(n_gpus=8, rank=2)
+    outs = []
+    try:
+        for ss, es, rows, wide in ((4, 4, 32, 33), (3, 3, 64, 0), (2, 4, 128, 129)):
+            tile_table.apply(lib, table(ss, es, rows, wide))
+            v = torch.zeros(T, 64, dtype=dtype, device=DEV)
+            ops.atmm(v, x, wa.view(total, 1, h), *tabs, idx, 0, sc, oc, rc, li, si, None, len(seg_len))
+            y = y0.clone()
+            ops.atmm(y, v, wb.view(total, 1, h), *tabs, idx, 0, sc, oc, rc, li, si, None, len(seg_len), apply_scale=True)
+            eng = LoraStepEngine([("p", 512, 768)], b4.ranks, b4.scalings(), dtype, DEV, 1, b4.T)
+            eng.randomize_weights(seed=64)
+            gg = torch.Generator(device=DEV)
+            gg.manual_seed(65)
+            eng.x[0][0].normal_(generator=gg)
+            eng.y[0][0].normal_(generator=gg)
+            eng.step(torch.from_numpy(b4.tok_adapter.astype(np.int64)).to(DEV))
+            torch.cuda.synchronize()
+            assert ops.device_status() == 0
+            outs.append((v.cpu(), y.cpu(), eng.y[0][0].cpu()))
+            del eng
+    finally:
+        tile_table.apply(lib, base)
+    for o in outs[1:]:
+        for a, b in zip(outs[0], o):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16))
