@@ -336,21 +336,24 @@ __device__ __forceinline__ SubLayout sub_layout(const TileInfo& ti, int n_pad, u
 // Gather tiles, where the activations are at least eight K blocks wide: a gathered row is
 // fetched g K blocks at a time with ONE copy (a [1 row x g blocks x 64 columns] box of the 3-D
 // view of the activations), which lands as g consecutive 128-byte lines.  Token i then owns
-// the lines i*g .. i*g+g-1 of the stage's X region, line i*g+j holding its K block j - and the
-// MMA, which takes line L for row L of a 128-row operand, multiplies the whole region with the
-// weights of K block j into accumulator j.  Of accumulator j only the rows L with L % g == j
-// mean anything (the others paired a token's block with another block's weights); the epilogue
-// picks those and adds the g of them that belong to a token.  One sixteenth to a quarter of the
-// copy instructions of one-row, one-block copies, which is what bounded these tiles.
-//   g = 8 accumulators of 32 columns (rank <= 32), 4 of 64 (rank <= 64), 2 of 128 - and no
-//   more than the 128 lines of the operand allow: 8 for tiles of up to 16 rows, else 4
+// the lines i*g .. i*g+g-1 of the stage's X region, line i*g+j holding its K block j.  The
+// stage's g weight blocks lie one behind the other, so they form ONE operand of g * n_pad
+// rows, and one MMA per 16-column K slice multiplies the whole X region with all of them:
+// accumulator columns j*n_pad .. j*n_pad+n_pad-1 pair every line with the weights of K block
+// j.  Of those only the lines L with L % g == j mean anything (the others paired a token's
+// block with another block's weights); the epilogue picks them and adds the g of them that
+// belong to a token.  One sixteenth to a quarter of the copy instructions of one-row,
+// one-block copies, and four MMAs per stage instead of 4 g: at 60-80 cycles per MMA for
+// the issuing thread, 256 narrow MMAs per tile had been what bounded these tiles below rank 128.
+//   g = 8 K blocks per stage (rank <= 32), 4 (rank <= 64), 2 above - and no more than the 128
+//   lines of the operand allow: 8 for tiles of up to 16 rows, else 4
 // Stage: [X region, cap * g lines][weights of block 0] .. [weights of block g-1]
 struct GatherLayout { int g, gsel, astr; uint32_t xbytes, wbytes; };
 __device__ __forceinline__ GatherLayout gather_layout(int n_pad, int rows) {
   GatherLayout gl;
   const int cap = gather_cap(rows);
-  gl.astr = n_pad <= 32 ? 32 : (n_pad <= 64 ? 64 : 128);
-  gl.g = min(256 / gl.astr, kTileM / cap);
+  gl.g = min(n_pad <= 32 ? 8 : (n_pad <= 64 ? 4 : 2), kTileM / cap);
+  gl.astr = n_pad;                                     // accumulator columns per K block
   gl.gsel = gl.g == 8 ? 2 : (gl.g == 4 ? 1 : 0);
   gl.xbytes = (uint32_t)(cap * gl.g) * 128u;
   gl.wbytes = (uint32_t)n_pad * 128u;
@@ -532,9 +535,11 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         ok = mbar_wait(tempty_bar(ab), ((li >> 1) & 1) ^ 1, &abort_s);
         if (ok) tc_fence_after();
         if (ti.gather && kblocks >= kGather3MinBlocks) {
-          // K block j of a stage goes to accumulator j, the whole X region as the A operand
+          // one MMA per K slice: the whole X region against the stage's weight blocks (N = nsub * n_pad)
           const GatherLayout gl = gather_layout(n_pad, ti.rows);
           const int nstages = (kblocks + gl.g - 1) / gl.g;
+          const bool bf = std::is_same<T, __nv_bfloat16>::value;
+          const uint32_t idesc_full = instr_desc_f16(bf, gl.g * n_pad, 0);
           for (int st = 0; st < nstages && ok; ++st, ++kiter) {
             const int s = kiter % nst;
             ok = mbar_wait(full_bar(s), (kiter / nst) & 1, &abort_s);
@@ -542,14 +547,22 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
             trace_stamp(src, kiter, 1);
             tc_fence_after();
             const int nsub = min(gl.g, kblocks - st * gl.g);
+            const uint32_t idesc_g = nsub == gl.g ? idesc_full : instr_desc_f16(bf, nsub * n_pad, 0);
             const uint64_t ad = smem_desc_sw128(x_stage(s), 16, 1024);
-            uint64_t bd = smem_desc_sw128(x_stage(s) + gl.xbytes, 16, 1024);
-            for (int j = 0; j < nsub; ++j) {
+            const uint64_t bd = smem_desc_sw128(x_stage(s) + gl.xbytes, 16, 1024);
+            if (n_pad <= 64) {
 #pragma unroll
               for (int k = 0; k < kBoxCols / 16; ++k)
-                umma_f16(tacc + (uint32_t)(j * gl.astr), ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc,
-                         (st > 0 || k > 0) ? 1u : 0u);
-              bd += (uint64_t)(gl.wbytes >> 4);
+                umma_f16(tacc, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc_g, (st > 0 || k > 0) ? 1u : 0u);
+            } else {
+              // two blocks of 80 .. 128 rows: an MMA each measured 6 % faster than one of N = 256
+              for (int j = 0; j < nsub; ++j) {
+                const uint64_t bj = bd + (uint64_t)j * (uint64_t)(gl.wbytes >> 4);
+#pragma unroll
+                for (int k = 0; k < kBoxCols / 16; ++k)
+                  umma_f16(tacc + (uint32_t)(j * gl.astr), ad + (uint64_t)(2 * k), bj + (uint64_t)(2 * k), idesc,
+                           (st > 0 || k > 0) ? 1u : 0u);
+              }
             }
             umma_commit(empty_bar(s));
             trace_stamp(src, kiter, 2);
@@ -1024,35 +1037,41 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
           // gathered rows, transposed product: warp (q, j) takes the chains j, j + 2, ... of 128
           // columns; within a chain this lane owns column q * 32 + lane and gets the row values
           // of that column from tensor memory, 16 rows at a time.  Row-major Y tile, tile_n
-          // columns wide.  The accumulator is handed back once this warp's last chunk is in
-          // registers.
+          // columns wide.
+          // Phase 1: out = y0 + scale * acc, rounded once, written back in place.  The
+          // accumulator is handed back once this warp's last chunk is in registers.
           const int nhalf = gather_cap(ti.rows) >> 4;
           const int cs = 16 * nhalf;                   // accumulator columns per chain
           const int nchains = er.ncbt >> 1;
           const uint32_t ytile = b_stage(s) + er.yoff;
           const uint32_t ypitch = (uint32_t)er.tile_n * 2u;
           for (int mt = j; mt < nchains; mt += 2) {
-            const int colt = mt * 128 + q * 32 + lane;
-            const int col = n0 + colt;
+            const uint32_t ycol = ytile + (uint32_t)(mt * 128 + q * 32 + lane) * 2u;
             for (int half = 0; half < nhalf; ++half) {
               uint32_t r[16];
-              uint32_t yv[16];
               tmem_ld_32x16(tacc + mt * cs + half * 16, r);
-#pragma unroll
-              for (int i = 0; i < 16; ++i) yv[i] = lds16(ytile + (half * 16 + i) * ypitch + colt * 2);
               tmem_ld_wait();
               if (mt + 2 >= nchains && half == nhalf - 1) {
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(ab));
               }
+              // four rows at a time, straight-line (a row slot past the tile's last row holds
+              // nothing that is stored later): the loads of a group go out together and the
+              // four chains of conversions overlap
+              const int nh = ti.rows - half * 16;      // rows of this half (the same for every lane)
+              uint32_t a = ycol + (uint32_t)(half * 16) * ypitch;
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int gi = __shfl_sync(0xffffffffu, grow_l, half * 16 + i);   // row i of this half
-                if (col < h_out && half * 16 + i < ti.rows) {
-                  const uint16_t y16 = (uint16_t)yv[i];
-                  const float y0 = Elem<T>::to_float(*reinterpret_cast<const T*>(&y16));
-                  y[(int64_t)gi * h_out + col] = Elem<T>::from_float(fmaf(scale, __uint_as_float(r[i]), y0));
+              for (int g4 = 0; g4 < 4; ++g4) {
+                if (g4 * 4 < nh) {
+                  uint32_t yv[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) yv[e] = lds16(a + (uint32_t)e * ypitch);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    sts16(a + (uint32_t)e * ypitch,
+                          Elem<T>::float_to_bits(fmaf(scale, __uint_as_float(r[g4 * 4 + e]), Elem<T>::bits_to_float(yv[e]))));
+                  a += 4u * ypitch;
                 }
               }
             }
@@ -1061,6 +1080,25 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(ab));
+          }
+          __syncwarp();
+          // Phase 2: the warp's own 64-byte pieces go out as 16-byte vectors, 8 rows per
+          // instruction; a chain's pieces are all read before the first one is stored
+          const int my_row = lane >> 2;
+          int gi[kGatherRows / 8];
+#pragma unroll
+          for (int g = 0; g < kGatherRows / 8; ++g) gi[g] = __shfl_sync(0xffffffffu, grow_l, g * 8 + my_row);
+          for (int mt = j; mt < nchains; mt += 2) {
+            const int colw = mt * 128 + q * 32 + (lane & 3) * 8;
+            const bool col_ok = n0 + colw < h_out;
+            const uint32_t src0 = ytile + (uint32_t)my_row * ypitch + (uint32_t)colw * 2u;
+            uint4 ov[kGatherRows / 8];
+#pragma unroll
+            for (int g = 0; g < kGatherRows / 8; ++g)
+              if (g * 8 < ti.rows) ov[g] = lds128(src0 + (uint32_t)(g * 8) * ypitch);
+#pragma unroll
+            for (int g = 0; g < kGatherRows / 8; ++g)
+              if (g * 8 + my_row < ti.rows && col_ok) stg128(y + (int64_t)gi[g] * h_out + n0 + colw, ov[g]);
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(empty_bar(s));

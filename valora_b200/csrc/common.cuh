@@ -26,6 +26,9 @@ struct Elem<__half> {
   }
   static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
+  // one element as the low 16 bits of a register
+  static __device__ __forceinline__ float bits_to_float(uint32_t u) { return __half2float(__ushort_as_half((unsigned short)u)); }
+  static __device__ __forceinline__ uint32_t float_to_bits(float v) { return __half_as_ushort(__float2half_rn(v)); }
 };
 
 template <>
@@ -43,6 +46,8 @@ struct Elem<__nv_bfloat16> {
   }
   static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float bits_to_float(uint32_t u) { return __uint_as_float(u << 16); }
+  static __device__ __forceinline__ uint32_t float_to_bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
 };
 
 // 128-bit global load through the read-only path, no L1 allocation: adapter

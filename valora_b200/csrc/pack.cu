@@ -18,6 +18,11 @@ namespace vlr {
 constexpr int kPackBlock = 256;      // tokens per histogram block
 constexpr int kPackMaxAdapters = 8192;
 constexpr int kScanThreads = 1024;
+// One CTA does the scans, so every pass over global memory costs the thread a full round trip per
+// dependent load: the passes load this many elements ahead of using them (registers: 64 per thread).
+constexpr int kScanAhead = 16;                         // pack_scan: blocks per adapter
+constexpr int kPosAhead = 8;                           // pack_tiles: sorted positions
+constexpr int kChunkAhead = 4;                         // pack_tiles: chunks
 constexpr int kPackFusedBits = 13;                     // row index bits of a sort key
 constexpr int kPackFusedTokens = 1024;                 // batches up to this size are packed by ONE launch
 static_assert(kPackFusedTokens <= (1 << kPackFusedBits) && kPackMaxAdapters <= (1 << (32 - kPackFusedBits - 1)),
@@ -29,10 +34,7 @@ struct PackWs {
   int32_t* key;         // [T] sorted keys
   int32_t* chunk_start; // [T+1]
   int32_t* chunk_seg;   // [T]
-  int32_t* chunk_tile;  // [T+1] exclusive tile prefix per chunk
-  int32_t* chunk_short; // [T+1] exclusive short-row prefix per chunk
-  int32_t* seg_chunk;   // [T+1] first chunk of each segment
-  int32_t* seg_gtile;   // [T+1] exclusive gather-tile prefix per segment
+  int32_t* seg_short;   // [T+1] exclusive short-row prefix per segment
   int32_t* gpos;        // [T] sorted position of each gather row
 };
 
@@ -51,12 +53,9 @@ static size_t pack_ws_layout(int64_t T, int64_t n_adapters, PackWs* ws, char* ba
   int32_t* key = take(T);
   int32_t* cs = take(T + 1);
   int32_t* cg = take(T);
-  int32_t* ct = take(T + 1);
-  int32_t* csh = take(T + 1);
-  int32_t* sc = take(T + 1);
-  int32_t* sg = take(T + 1);
+  int32_t* ssh = take(T + 1);
   int32_t* gp = take(T);
-  if (ws) *ws = PackWs{hist, abase, key, cs, cg, ct, csh, sc, sg, gp};
+  if (ws) *ws = PackWs{hist, abase, key, cs, cg, ssh, gp};
   return off;
 }
 
@@ -111,11 +110,16 @@ pack_scan_kernel(int nblk, int n_adapters, int32_t* hist, int32_t* abase) {
   // per-adapter exclusive prefix over blocks; the adapter's total lands in abase
   for (int a = threadIdx.x; a < n_adapters; a += kScanThreads) {
     int run = 0;
-    for (int b = 0; b < nblk; ++b) {
-      int32_t* p = hist + (int64_t)b * n_adapters + a;
-      const int c = *p;
-      *p = run;
-      run += c;
+    for (int b0 = 0; b0 < nblk; b0 += kScanAhead) {
+      int c[kScanAhead];
+#pragma unroll
+      for (int j = 0; j < kScanAhead; ++j)
+        c[j] = b0 + j < nblk ? hist[(int64_t)(b0 + j) * n_adapters + a] : 0;
+#pragma unroll
+      for (int j = 0; j < kScanAhead; ++j) {
+        if (b0 + j < nblk) hist[(int64_t)(b0 + j) * n_adapters + a] = run;
+        run += c[j];
+      }
     }
     abase[a] = run;
   }
@@ -221,36 +225,60 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
   const int32_t* key = ws.key;
   const int32_t* row = out.perm;
 
-  // ---- pass 1: segment and chunk boundaries over sorted positions
+  // ---- pass 1: segment and chunk boundaries over sorted positions.  A chunk is a maximal run of
+  // consecutive batch rows inside a segment.
   {
     const int per = (T + kScanThreads - 1) / kScanThreads;
     const int lo = min(tid * per, T), hi = min(lo + per, T);
+    // keys and rows of positions b0-1 .. b0+kPosAhead-1 (position -1 reads as "no adapter")
+    auto load = [&](int b0, int (&kk)[kPosAhead + 1], int (&rr)[kPosAhead + 1]) {
+#pragma unroll
+      for (int j = 0; j <= kPosAhead; ++j) {
+        const int i = b0 - 1 + j;
+        const bool ok = i >= 0 && i < hi;
+        kk[j] = ok ? key[i] : -1;
+        rr[j] = ok ? row[i] : -2;
+      }
+    };
     int nseg = 0, nchunk = 0;
-    for (int i = lo; i < hi; ++i) {
-      const bool sflag = i == 0 || key[i] != key[i - 1];
-      const bool cflag = sflag || row[i] != row[i - 1] + 1;
-      nseg += sflag;
-      nchunk += cflag;
+    for (int b0 = lo; b0 < hi; b0 += kPosAhead) {
+      int kk[kPosAhead + 1], rr[kPosAhead + 1];
+      load(b0, kk, rr);
+#pragma unroll
+      for (int j = 1; j <= kPosAhead; ++j) {
+        if (b0 - 1 + j < hi) {
+          const bool sflag = kk[j] != kk[j - 1];
+          nseg += sflag;
+          nchunk += sflag || rr[j] != rr[j - 1] + 1;
+        }
+      }
     }
     int P, C;
     int sbase = block_exscan(nseg, &P, warp_sums);
     int cbase = block_exscan(nchunk, &C, warp_sums);
     if (tid == 0) { s_P = P; s_C = C; }
-    for (int i = lo; i < hi; ++i) {
-      const bool sflag = i == 0 || key[i] != key[i - 1];
-      const bool cflag = sflag || row[i] != row[i - 1] + 1;
-      if (sflag) {
-        const int a = key[i];
-        out.seg_start[sbase] = i;
-        out.seg_adapter[sbase] = a;
-        out.seg_rank[sbase] = a_len[a] / 4;
-        ws.seg_chunk[sbase] = cbase;
-        ++sbase;
-      }
-      if (cflag) {
-        ws.chunk_start[cbase] = i;
-        ws.chunk_seg[cbase] = sbase - 1;
-        ++cbase;
+    for (int b0 = lo; b0 < hi; b0 += kPosAhead) {
+      int kk[kPosAhead + 1], rr[kPosAhead + 1];
+      load(b0, kk, rr);
+#pragma unroll
+      for (int j = 1; j <= kPosAhead; ++j) {
+        const int i = b0 - 1 + j;
+        if (i < hi) {
+          const bool sflag = kk[j] != kk[j - 1];
+          const bool cflag = sflag || rr[j] != rr[j - 1] + 1;
+          if (sflag) {
+            const int a = kk[j];
+            out.seg_start[sbase] = i;
+            out.seg_adapter[sbase] = a;
+            out.seg_rank[sbase] = a_len[a] / 4;
+            ++sbase;
+          }
+          if (cflag) {
+            ws.chunk_start[cbase] = i;
+            ws.chunk_seg[cbase] = sbase - 1;
+            ++cbase;
+          }
+        }
       }
     }
   }
@@ -259,7 +287,6 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
   if (tid == 0) {
     out.seg_start[P] = T;
     ws.chunk_start[C] = T;
-    ws.seg_chunk[P] = C;
   }
   __syncthreads();
   for (int s = tid; s < P; s += kScanThreads) out.seg_len[s] = out.seg_start[s + 1] - out.seg_start[s];
@@ -270,36 +297,57 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     const int per = (C + kScanThreads - 1) / kScanThreads;
     const int lo = min(tid * per, C), hi = min(lo + per, C);
     int nt = 0, ns = 0;
-    for (int c = lo; c < hi; ++c) {
-      const int len = ws.chunk_start[c + 1] - ws.chunk_start[c];
-      if (len >= mma_min) nt += (len + tile_m - 1) / tile_m; else ns += len;
+    for (int b0 = lo; b0 < hi; b0 += kChunkAhead) {
+      int cs[kChunkAhead + 1];
+#pragma unroll
+      for (int j = 0; j <= kChunkAhead; ++j) cs[j] = ws.chunk_start[min(b0 + j, hi)];
+#pragma unroll
+      for (int j = 0; j < kChunkAhead; ++j) {
+        const int len = cs[j + 1] - cs[j];           // 0 past the thread's range
+        if (len >= mma_min) nt += (len + tile_m - 1) / tile_m; else ns += len;
+      }
     }
     int tbase = block_exscan(nt, &n_mma, warp_sums);
     int shbase = block_exscan(ns, &n_short, warp_sums);
-    for (int c = lo; c < hi; ++c) {
-      const int start = ws.chunk_start[c];
-      const int len = ws.chunk_start[c + 1] - start;
-      ws.chunk_tile[c] = tbase;
-      ws.chunk_short[c] = shbase;
-      const int seg = ws.chunk_seg[c];
-      const int a = key[start];
-      if (len >= mma_min) {
-        const int rank = (int)(a_len[a] / 4);
-        for (int m0 = 0; m0 < len; m0 += tile_m, ++tbase) {
-          if (tbase < out.tiles_cap) {
-            int32_t* t = out.tiles + (int64_t)tbase * VLR_TILE_INTS;
-            t[0] = VLR_TILE_MMA; t[1] = a; t[2] = rank; t[3] = row[start + m0];
-            t[4] = min(tile_m, len - m0); t[5] = seg; t[6] = start + m0; t[7] = 0;
+    for (int b0 = lo; b0 < hi; b0 += kChunkAhead) {
+      int cs[kChunkAhead + 1], sg[kChunkAhead + 1], ka[kChunkAhead], r0[kChunkAhead];
+#pragma unroll
+      for (int j = 0; j <= kChunkAhead; ++j) cs[j] = ws.chunk_start[min(b0 + j, hi)];
+#pragma unroll
+      for (int j = 0; j <= kChunkAhead; ++j) {       // sg[j]: segment of chunk b0 + j - 1
+        const int c = b0 + j - 1;
+        sg[j] = (c >= 0 && c < hi) ? ws.chunk_seg[c] : -1;
+      }
+#pragma unroll
+      for (int j = 0; j < kChunkAhead; ++j) {
+        const bool ok = b0 + j < hi;
+        ka[j] = ok ? key[cs[j]] : 0;
+        r0[j] = ok ? row[cs[j]] : 0;
+      }
+#pragma unroll
+      for (int j = 0; j < kChunkAhead; ++j) {
+        if (b0 + j < hi) {
+          const int start = cs[j], len = cs[j + 1] - cs[j], seg = sg[j + 1], a = ka[j];
+          if (seg != sg[j]) ws.seg_short[seg] = shbase;   // first chunk of its segment
+          if (len >= mma_min) {
+            const int rank = (int)(a_len[a] / 4);
+            for (int m0 = 0; m0 < len; m0 += tile_m, ++tbase) {
+              if (tbase < out.tiles_cap) {
+                int32_t* t = out.tiles + (int64_t)tbase * VLR_TILE_INTS;
+                t[0] = VLR_TILE_MMA; t[1] = a; t[2] = rank; t[3] = r0[j] + m0;   // a chunk's rows are consecutive
+                t[4] = min(tile_m, len - m0); t[5] = seg; t[6] = start + m0; t[7] = 0;
+              }
+            }
+          } else {
+            for (int k = 0; k < len; ++k, ++shbase) {
+              out.gather_rows[shbase] = r0[j] + k;
+              ws.gpos[shbase] = start + k;
+            }
           }
-        }
-      } else {
-        for (int k = 0; k < len; ++k, ++shbase) {
-          out.gather_rows[shbase] = row[start + k];
-          ws.gpos[shbase] = start + k;
         }
       }
     }
-    if (tid == 0) { ws.chunk_tile[C] = n_mma; ws.chunk_short[C] = n_short; }
+    if (tid == 0) ws.seg_short[P] = n_short;
   }
   __syncthreads();
 
@@ -309,15 +357,11 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     const int per = (P + kScanThreads - 1) / kScanThreads;
     const int lo = min(tid * per, P), hi = min(lo + per, P);
     int ng = 0;
-    for (int s = lo; s < hi; ++s) {
-      const int cnt = ws.chunk_short[ws.seg_chunk[s + 1]] - ws.chunk_short[ws.seg_chunk[s]];
-      ng += (cnt + grp - 1) / grp;
-    }
+    for (int s = lo; s < hi; ++s) ng += (ws.seg_short[s + 1] - ws.seg_short[s] + grp - 1) / grp;
     int gbase = block_exscan(ng, &n_gather, warp_sums);
     for (int s = lo; s < hi; ++s) {
-      const int first = ws.chunk_short[ws.seg_chunk[s]];
-      const int cnt = ws.chunk_short[ws.seg_chunk[s + 1]] - first;
-      ws.seg_gtile[s] = gbase;
+      const int first = ws.seg_short[s];
+      const int cnt = ws.seg_short[s + 1] - first;
       const int a = (int)out.seg_adapter[s];
       const int rank = (int)out.seg_rank[s];
       for (int g0 = 0; g0 < cnt; g0 += grp, ++gbase) {

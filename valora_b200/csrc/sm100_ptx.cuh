@@ -227,10 +227,14 @@ __device__ __forceinline__ uint32_t instr_desc_f16(int is_bf16, int n, int b_mn_
   return d;
 }
 
+// 16-bit shared-memory accesses through 32-bit registers (zero-extended / truncated)
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
+}
+__device__ __forceinline__ void sts16(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;

@@ -431,6 +431,12 @@ def trace_step(config: int, layers: int, phase: str, dev):
         out["operands_seen_to_epilogue_start_median"] = med(2, 1)
         out["epilogue_median"] = med(3, 2)
         out["issue_to_handed_back_median"] = med(3, 0)
+        g = t[1:][t[1:, 4] > 0]                          # stages of gather tiles stamp their epilogue's phases
+        if len(g):
+            out["gather_stages"] = int(len(g))
+            out["gather_epilogue_first_chunk_read_median"] = int(np.median(g[:, 4] - g[:, 2]))
+            out["gather_epilogue_combine_median"] = int(np.median(g[:, 5] - g[:, 4]))
+            out["gather_epilogue_store_median"] = int(np.median(g[:, 3] - g[:, 5]))
     return out
 
 
