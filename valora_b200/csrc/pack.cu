@@ -177,6 +177,7 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
   __shared__ int s_P, s_C;
   const int tid = threadIdx.x;
   extern __shared__ uint32_t sort_keys[];              // sorted == 2 only: the batch's (adapter, row) keys
+  const int32_t* s_row = out.perm;                     // rows in sorted order
 
   // every count is written by this kernel (nothing has to be cleared ahead of it); the
   // status starts from the ids themselves
@@ -216,14 +217,26 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
         __syncthreads();
       }
     }
+    // Everything the passes below write and read again lives in shared memory here (this
+    // one CTA is the only reader): no pass waits for a round trip to L2.
+    int32_t* sm = reinterpret_cast<int32_t*>(sort_keys + n2);
+    ws.key = sm;
+    int32_t* rows_sm = sm + T;
+    s_row = rows_sm;
+    ws.chunk_start = sm + 2 * T;
+    ws.chunk_seg = ws.chunk_start + (T + 1);
+    ws.seg_short = ws.chunk_seg + T;
+    ws.gpos = ws.seg_short + (T + 1);
     for (int i = tid; i < T; i += kScanThreads) {
-      out.perm[i] = (int32_t)(sort_keys[i] & ((1u << kPackFusedBits) - 1u));
+      const int32_t r = (int32_t)(sort_keys[i] & ((1u << kPackFusedBits) - 1u));
+      out.perm[i] = r;
+      rows_sm[i] = r;
       ws.key[i] = (int32_t)(sort_keys[i] >> kPackFusedBits);
     }
     __syncthreads();
   }
   const int32_t* key = ws.key;
-  const int32_t* row = out.perm;
+  const int32_t* row = s_row;
 
   // ---- pass 1: segment and chunk boundaries over sorted positions.  A chunk is a maximal run of
   // consecutive batch rows inside a segment.
@@ -392,7 +405,7 @@ static int pack_launch(const int64_t* tok_adapter, int64_t T, const int64_t* a_l
   if (sort && T > 0 && T <= kPackFusedTokens) {
     int n2 = 32;
     while (n2 < T) n2 <<= 1;
-    pack_tiles_kernel<<<1, kScanThreads, n2 * sizeof(uint32_t), s>>>(tok_adapter, a_len, (int)T, (int)n_adapters, 2,
+    pack_tiles_kernel<<<1, kScanThreads, (n2 + 6 * T + 2) * sizeof(uint32_t), s>>>(tok_adapter, a_len, (int)T, (int)n_adapters, 2,
                                                                      tile_m, mma_min_rows, gather_rows_per_tile,
                                                                      ws, out);
     return launch_status();
