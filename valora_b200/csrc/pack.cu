@@ -7,7 +7,8 @@
 //   1. pack_hist     per-block adapter histograms (blocks of kPackBlock tokens)
 //   2. pack_scan     per-adapter exclusive prefix over blocks + adapter bases
 //   3. pack_scatter  stable placement: perm and the sorted key array
-//   4. pack_tiles    segments, chunks and the tile schedule (one CTA)
+//   4. pack_tiles    segments, chunks and the tile schedule (one CTA; its working arrays in shared
+//                    memory up to 16384 rows, in the workspace above)
 // In reference order (sort = 0) only the last one runs.
 #include <mutex>
 
@@ -18,6 +19,7 @@ namespace vlr {
 constexpr int kPackBlock = 256;      // tokens per histogram block
 constexpr int kPackMaxAdapters = 8192;
 constexpr int kScanThreads = 1024;
+constexpr int kMaxDevices = 64;
 // One CTA does the scans, so every pass over global memory costs the thread a full round trip per
 // dependent load: the passes load this many elements ahead of using them (registers: 64 per thread).
 constexpr int kScanAhead = 16;                         // pack_scan: blocks per adapter
@@ -25,6 +27,7 @@ constexpr int kPosAhead = 8;                           // pack_tiles: sorted pos
 constexpr int kChunkAhead = 4;                         // pack_tiles: chunks
 constexpr int kPackFusedBits = 13;                     // row index bits of a sort key
 constexpr int kPackFusedTokens = 1024;                 // batches up to this size are packed by ONE launch
+constexpr int kPackSmemTokens = 16384;                 // up to this size pack_tiles works in shared memory (2-byte indices)
 static_assert(kPackFusedTokens <= (1 << kPackFusedBits) && kPackMaxAdapters <= (1 << (32 - kPackFusedBits - 1)),
               "adapter id and row index must fit one 32-bit sort key below the padding value");
 
@@ -169,15 +172,55 @@ struct PackOut {
 
 // One CTA.  Thread t owns the contiguous index range [t*per, (t+1)*per) of
 // whatever is being scanned (sorted positions, chunks, segments).
+// I = the type of the arrays the passes write and read again (sorted keys and rows, chunk
+// starts, chunk segments, short-row prefixes, gather positions).  uint16_t: batches of up to
+// kPackSmemTokens rows keep them in shared memory - this one CTA is their only reader, so no
+// pass waits for a round trip to L2 (at 16384 rows the kernel took 63 us on the workspace, 43 us so).
+// int32_t: larger batches keep them in the workspace.
+// An array of pack_tiles.  In shared memory (2-byte elements) thread t walks the elements
+// t*per .. t*per+per-1, so at 16 elements per thread the lanes of a warp are 32 bytes apart and
+// eight of them meet in every bank: one word of padding per 16 elements spreads them over
+// all banks (the tile pass 48 -> 43 us at 16384 rows).
+template <typename I>
+struct PackArr {
+  I* p;
+  __device__ __forceinline__ I& operator[](int i) const { return p[sizeof(I) == 2 ? i + ((i >> 4) << 1) : i]; }
+};
+__host__ __device__ inline int pack_arr_len(int n) { return n + ((n >> 4) << 1) + 2; }
+
+template <typename I>
 __global__ void __launch_bounds__(kScanThreads)
 pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a_len, int T,
                   int n_adapters, int sorted, int tile_m, int mma_min, int grp, PackWs ws,
                   PackOut out) {
+  constexpr bool kSmem = sizeof(I) == 2;
   __shared__ int warp_sums[33];
   __shared__ int s_P, s_C;
   const int tid = threadIdx.x;
-  extern __shared__ uint32_t sort_keys[];              // sorted == 2 only: the batch's (adapter, row) keys
-  const int32_t* s_row = out.perm;                     // rows in sorted order
+  extern __shared__ uint32_t sort_keys[];              // sorted == 2: the batch's (adapter, row) keys come first
+  int n2 = 0;
+  if (sorted == 2) {
+    n2 = 32;
+    while (n2 < T) n2 <<= 1;
+  }
+  PackArr<I> key_a, row_a, cs_a, cg_a, ssh_a, gp_a;
+  if constexpr (kSmem) {
+    I* sm = reinterpret_cast<I*>(sort_keys + n2);
+    const int cap = pack_arr_len(T + 1);
+    key_a.p = sm;
+    row_a.p = sm + cap;
+    cs_a.p = sm + 2 * cap;
+    cg_a.p = sm + 3 * cap;
+    ssh_a.p = sm + 4 * cap;
+    gp_a.p = sm + 5 * cap;
+  } else {
+    key_a.p = ws.key;
+    row_a.p = out.perm;
+    cs_a.p = ws.chunk_start;
+    cg_a.p = ws.chunk_seg;
+    ssh_a.p = ws.seg_short;
+    gp_a.p = ws.gpos;
+  }
 
   // every count is written by this kernel (nothing has to be cleared ahead of it); the
   // status starts from the ids themselves
@@ -185,9 +228,13 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
   for (int i = tid; i < T; i += kScanThreads) {
     const int64_t id = tok[i];
     bad |= (id < 0 || id >= n_adapters) ? 1 : 0;
-    if (!sorted) {
+    if (sorted == 0) {                                 // reference order: identity permutation
       out.perm[i] = i;
-      ws.key[i] = clamp_id(id, n_adapters);
+      key_a[i] = (I)clamp_id(id, n_adapters);
+      if constexpr (kSmem) row_a[i] = (I)i;
+    } else if (kSmem && sorted == 1) {                 // what pack_scatter placed, brought on chip
+      key_a[i] = (I)ws.key[i];
+      row_a[i] = (I)out.perm[i];
     }
   }
   bad = __syncthreads_or(bad);
@@ -197,8 +244,6 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     // takes longer than those launches.  A bitonic sort in shared memory of (adapter << 13 | row),
     // which orders by adapter and keeps the batch order inside an adapter - the same
     // permutation as the stable counting sort, bit for bit.
-    int n2 = 32;
-    while (n2 < T) n2 <<= 1;
     for (int i = tid; i < n2; i += kScanThreads)
       sort_keys[i] = i < T ? ((uint32_t)clamp_id(tok[i], n_adapters) << kPackFusedBits) | (uint32_t)i : 0xffffffffu;
     __syncthreads();
@@ -217,26 +262,15 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
         __syncthreads();
       }
     }
-    // Everything the passes below write and read again lives in shared memory here (this
-    // one CTA is the only reader): no pass waits for a round trip to L2.
-    int32_t* sm = reinterpret_cast<int32_t*>(sort_keys + n2);
-    ws.key = sm;
-    int32_t* rows_sm = sm + T;
-    s_row = rows_sm;
-    ws.chunk_start = sm + 2 * T;
-    ws.chunk_seg = ws.chunk_start + (T + 1);
-    ws.seg_short = ws.chunk_seg + T;
-    ws.gpos = ws.seg_short + (T + 1);
     for (int i = tid; i < T; i += kScanThreads) {
       const int32_t r = (int32_t)(sort_keys[i] & ((1u << kPackFusedBits) - 1u));
       out.perm[i] = r;
-      rows_sm[i] = r;
-      ws.key[i] = (int32_t)(sort_keys[i] >> kPackFusedBits);
+      if constexpr (kSmem) row_a[i] = (I)r;
+      key_a[i] = (I)(sort_keys[i] >> kPackFusedBits);
     }
     __syncthreads();
   }
-  const int32_t* key = ws.key;
-  const int32_t* row = s_row;
+  const PackArr<I> key = key_a, row = row_a;
 
   // ---- pass 1: segment and chunk boundaries over sorted positions.  A chunk is a maximal run of
   // consecutive batch rows inside a segment.
@@ -287,8 +321,8 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
             ++sbase;
           }
           if (cflag) {
-            ws.chunk_start[cbase] = i;
-            ws.chunk_seg[cbase] = sbase - 1;
+            cs_a[cbase] = i;
+            cg_a[cbase] = sbase - 1;
             ++cbase;
           }
         }
@@ -299,7 +333,7 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
   const int P = s_P, C = s_C;
   if (tid == 0) {
     out.seg_start[P] = T;
-    ws.chunk_start[C] = T;
+    cs_a[C] = T;
   }
   __syncthreads();
   for (int s = tid; s < P; s += kScanThreads) out.seg_len[s] = out.seg_start[s + 1] - out.seg_start[s];
@@ -313,7 +347,7 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     for (int b0 = lo; b0 < hi; b0 += kChunkAhead) {
       int cs[kChunkAhead + 1];
 #pragma unroll
-      for (int j = 0; j <= kChunkAhead; ++j) cs[j] = ws.chunk_start[min(b0 + j, hi)];
+      for (int j = 0; j <= kChunkAhead; ++j) cs[j] = cs_a[min(b0 + j, hi)];
 #pragma unroll
       for (int j = 0; j < kChunkAhead; ++j) {
         const int len = cs[j + 1] - cs[j];           // 0 past the thread's range
@@ -325,11 +359,11 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     for (int b0 = lo; b0 < hi; b0 += kChunkAhead) {
       int cs[kChunkAhead + 1], sg[kChunkAhead + 1], ka[kChunkAhead], r0[kChunkAhead];
 #pragma unroll
-      for (int j = 0; j <= kChunkAhead; ++j) cs[j] = ws.chunk_start[min(b0 + j, hi)];
+      for (int j = 0; j <= kChunkAhead; ++j) cs[j] = cs_a[min(b0 + j, hi)];
 #pragma unroll
       for (int j = 0; j <= kChunkAhead; ++j) {       // sg[j]: segment of chunk b0 + j - 1
         const int c = b0 + j - 1;
-        sg[j] = (c >= 0 && c < hi) ? ws.chunk_seg[c] : -1;
+        sg[j] = (c >= 0 && c < hi) ? cg_a[c] : -1;
       }
 #pragma unroll
       for (int j = 0; j < kChunkAhead; ++j) {
@@ -341,7 +375,7 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
       for (int j = 0; j < kChunkAhead; ++j) {
         if (b0 + j < hi) {
           const int start = cs[j], len = cs[j + 1] - cs[j], seg = sg[j + 1], a = ka[j];
-          if (seg != sg[j]) ws.seg_short[seg] = shbase;   // first chunk of its segment
+          if (seg != sg[j]) ssh_a[seg] = shbase;   // first chunk of its segment
           if (len >= mma_min) {
             const int rank = (int)(a_len[a] / 4);
             for (int m0 = 0; m0 < len; m0 += tile_m, ++tbase) {
@@ -354,13 +388,13 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
           } else {
             for (int k = 0; k < len; ++k, ++shbase) {
               out.gather_rows[shbase] = r0[j] + k;
-              ws.gpos[shbase] = start + k;
+              gp_a[shbase] = start + k;
             }
           }
         }
       }
     }
-    if (tid == 0) ws.seg_short[P] = n_short;
+    if (tid == 0) ssh_a[P] = n_short;
   }
   __syncthreads();
 
@@ -370,11 +404,11 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
     const int per = (P + kScanThreads - 1) / kScanThreads;
     const int lo = min(tid * per, P), hi = min(lo + per, P);
     int ng = 0;
-    for (int s = lo; s < hi; ++s) ng += (ws.seg_short[s + 1] - ws.seg_short[s] + grp - 1) / grp;
+    for (int s = lo; s < hi; ++s) ng += (ssh_a[s + 1] - ssh_a[s] + grp - 1) / grp;
     int gbase = block_exscan(ng, &n_gather, warp_sums);
     for (int s = lo; s < hi; ++s) {
-      const int first = ws.seg_short[s];
-      const int cnt = ws.seg_short[s + 1] - first;
+      const int first = ssh_a[s];
+      const int cnt = ssh_a[s + 1] - first;
       const int a = (int)out.seg_adapter[s];
       const int rank = (int)out.seg_rank[s];
       for (int g0 = 0; g0 < cnt; g0 += grp, ++gbase) {
@@ -382,7 +416,7 @@ pack_tiles_kernel(const int64_t* __restrict__ tok, const int64_t* __restrict__ a
         if (ti < out.tiles_cap) {
           int32_t* t = out.tiles + ti * VLR_TILE_INTS;
           t[0] = VLR_TILE_GATHER; t[1] = a; t[2] = rank; t[3] = first + g0;
-          t[4] = min(grp, cnt - g0); t[5] = s; t[6] = ws.gpos[first + g0]; t[7] = 0;
+          t[4] = min(grp, cnt - g0); t[5] = s; t[6] = gp_a[first + g0]; t[7] = 0;
         }
       }
     }
@@ -402,12 +436,28 @@ static int pack_launch(const int64_t* tok_adapter, int64_t T, const int64_t* a_l
                        int sort, int tile_m, int mma_min_rows, int gather_rows_per_tile,
                        const PackWs& ws, const PackOut& out, cudaStream_t s) {
   const int nblk = (int)((T + kPackBlock - 1) / kPackBlock);
+  // the on-chip form of pack_tiles needs more than the default 48 KB of dynamic shared memory
+  const size_t smem_arrays = (size_t)6 * pack_arr_len((int)T + 1) * sizeof(uint16_t);
+  if (T <= kPackSmemTokens) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return VLR_ERR_RANGE;
+    static std::mutex mu;
+    static bool raised[kMaxDevices];
+    std::lock_guard<std::mutex> lock(mu);
+    if (!raised[dev]) {
+      e = cudaFuncSetAttribute((const void*)pack_tiles_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)(6 * pack_arr_len(kPackSmemTokens + 1) * sizeof(uint16_t) + 4 * kPackFusedTokens));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      raised[dev] = true;
+    }
+  }
   if (sort && T > 0 && T <= kPackFusedTokens) {
     int n2 = 32;
     while (n2 < T) n2 <<= 1;
-    pack_tiles_kernel<<<1, kScanThreads, (n2 + 6 * T + 2) * sizeof(uint32_t), s>>>(tok_adapter, a_len, (int)T, (int)n_adapters, 2,
-                                                                     tile_m, mma_min_rows, gather_rows_per_tile,
-                                                                     ws, out);
+    pack_tiles_kernel<uint16_t><<<1, kScanThreads, n2 * sizeof(uint32_t) + smem_arrays, s>>>(
+        tok_adapter, a_len, (int)T, (int)n_adapters, 2, tile_m, mma_min_rows, gather_rows_per_tile, ws, out);
     return launch_status();
   }
   if (sort && T > 0) {
@@ -417,9 +467,12 @@ static int pack_launch(const int64_t* tok_adapter, int64_t T, const int64_t* a_l
     pack_scatter_kernel<<<nblk, kPackBlock, 0, s>>>(tok_adapter, (int)T, (int)n_adapters, ws.hist,
                                                     ws.abase, out.perm, ws.key);
   }
-  pack_tiles_kernel<<<1, kScanThreads, 0, s>>>(tok_adapter, a_len, (int)T, (int)n_adapters,
-                                               sort && T > 0, tile_m, mma_min_rows,
-                                               gather_rows_per_tile, ws, out);
+  if (T <= kPackSmemTokens)
+    pack_tiles_kernel<uint16_t><<<1, kScanThreads, smem_arrays, s>>>(
+        tok_adapter, a_len, (int)T, (int)n_adapters, sort && T > 0, tile_m, mma_min_rows, gather_rows_per_tile, ws, out);
+  else
+    pack_tiles_kernel<int32_t><<<1, kScanThreads, 0, s>>>(
+        tok_adapter, a_len, (int)T, (int)n_adapters, sort && T > 0, tile_m, mma_min_rows, gather_rows_per_tile, ws, out);
   return launch_status();
 }
 
@@ -517,7 +570,6 @@ constexpr size_t kStaticScratchBytes = 1u << 20;
 
 static __device__ __align__(256) unsigned char g_pack_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 static std::mutex g_scratch_mu;
 static unsigned char* g_scratch_ptr[kMaxDevices];   // device address of g_pack_scratch, per device
 
