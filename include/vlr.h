@@ -332,6 +332,13 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
  * first: every gather tile takes the wide form (measurements, tests). */
 #define VLR_STEP_WIDE_GATHER_STAGES 32
 #define VLR_STEP_ALL_WIDE_GATHER_STAGES 64
+/* or-ed into phase_mask.  With max_rank above 64: each tensor-core kernel is launched twice,
+ * once over the tiles of adapters of rank <= 64 and once over the others, so that the first
+ * launch cuts its 192 KB operand ring for those ranks (four stages) instead of for the
+ * largest rank of the step (three): in a batch of mixed ranks the tiles up to rank 64 ran
+ * 18-34 % slower on the three-stage ring.  Set it when adapters of both classes are
+ * resident; same results bit for bit. */
+#define VLR_STEP_SPLIT_RANK_CLASSES 128
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,
                   const int32_t* counts, const void* scales, int max_h_in, int max_h_out,

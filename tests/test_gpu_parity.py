@@ -1074,3 +1074,34 @@ def test_results_do_not_depend_on_the_tile_table(ops):
     for o in outs[1:]:
         for a, b in zip(outs[0], o):
             assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+def test_rank_class_split_changes_nothing(ops):
+    """With adapters on both sides of rank 64 resident a step launches each tensor-core kernel
+    once per rank class (VLR_STEP_SPLIT_RANK_CLASSES).  Every tile is taken by exactly one of
+    the two launches: the results equal those of the single launch bit for bit, and a rank the
+    kernels do not support is still reported."""
+    from valora_b200.engine import LoraStepEngine
+    dtype = torch.bfloat16
+    b4 = workloads.config4(n_gpus=8, rank=5)
+    assert min(b4.ranks) <= 64 < max(b4.ranks)
+    tok = torch.from_numpy(b4.tok_adapter.astype(np.int64)).to(DEV)
+    outs = []
+    for split in (True, False):
+        eng = LoraStepEngine([("p", 1024, 512), ("q", 512, 1024)], b4.ranks, b4.scalings(), dtype, DEV, 2, b4.T,
+                             split_rank_classes=split)
+        assert bool(eng._gather_flag() & ops.STEP_SPLIT_RANK_CLASSES) == split
+        eng.randomize_weights(seed=71)
+        gg = torch.Generator(device=DEV)
+        gg.manual_seed(72)
+        for l in range(2):
+            for p in range(2):
+                eng.x[l][p].normal_(generator=gg)
+                eng.y[l][p].normal_(generator=gg)
+        eng.step(tok)
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        outs.append([eng.y[l][p].cpu() for l in range(2) for p in range(2)])
+        del eng
+    for a, b in zip(*outs):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))

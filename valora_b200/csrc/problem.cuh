@@ -78,6 +78,10 @@ struct TileSource {
   int wide_below_rank;               // expand: gather tiles of adapters below this rank use wide stages.  The
                                      // caller presets 0 (none), 1 (the tile table's threshold) or -1 (all tiles);
                                      // the launcher resolves it
+  // A step may run a kernel twice, once per rank class, so that each launch cuts its operand
+  // ring for the ranks it meets: tiles of a (valid) rank <= skip_ranks_upto, or > skip_ranks_above,
+  // belong to the other launch and are passed over silently.  0 = no such bound.
+  int skip_ranks_upto, skip_ranks_above;
   // adapter tables
   const int64_t* a_start;
   const int64_t* a_loc;

@@ -3,10 +3,39 @@
 // shrink and the expand of every problem of a packed batch.
 #include <string.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "problem.cuh"
 
 using namespace vlr;
+
+namespace {
+// A second stream per device for the steps that run their kernels once per rank class, with
+// the two events that fork it from and join it to the caller's stream.  Created on first use.
+struct SideStream {
+  cudaStream_t stream;
+  cudaEvent_t fork, join;
+};
+SideStream* side_stream() {
+  constexpr int kMaxDev = 64;
+  static std::mutex mu;
+  static SideStream slots[kMaxDev];
+  static bool made[kMaxDev];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!made[dev]) {
+    SideStream ss{};
+    if (cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&ss.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    slots[dev] = ss;
+    made[dev] = true;
+  }
+  return &slots[dev];
+}
+}  // namespace
 
 extern "C" size_t vlr_step_plan_bytes(int n_problems) {
   return n_problems > 0 ? (size_t)n_problems * sizeof(StepProblem) : 0;
@@ -61,7 +90,7 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   if ((reinterpret_cast<uintptr_t>(plan_dev) & 127u) != 0) return VLR_ERR_ALIGN;
   char* vb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
   const size_t need = (size_t)n_problems * (size_t)T * kMaxRank * 2;
-  const size_t need_all = ((need + 255) & ~size_t(255)) + 256;     // + two work-item counters, 128 bytes apart
+  const size_t need_all = ((need + 255) & ~size_t(255)) + 256;     // + four work-item counters, 64 bytes apart
   if ((size_t)(vb - reinterpret_cast<char*>(workspace)) + need_all > workspace_bytes) return VLR_ERR_WORKSPACE;
   unsigned int* counters = reinterpret_cast<unsigned int*>(vb + ((need + 255) & ~size_t(255)));
   // every tile holds at least one row
@@ -105,22 +134,58 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   // projection is narrower than the rank buffer must still go the right way.
   const int shrink_h_in = (int)max_h_in > kMaxRank ? (int)max_h_in : kMaxRank;
   const int expand_h_out = (int)max_h_out > kMaxRank ? (int)max_h_out : kMaxRank + 8;
+  // With adapters on both sides of rank 64, a kernel runs once per rank class: the launch for
+  // ranks <= 64 then has the four-stage ring those tiles are fastest on.  The classes share no
+  // adapter, so shrink and expand of one class depend on nothing of the other: the second
+  // class runs on a side stream, its CTAs moving onto the SMs as the first class's kernels
+  // run out of tiles (one tail per step instead of one per launch - with two tails config 2's
+  // large prefill tiles lost more than the deeper ring gained).
+  const bool split = (phase_mask & VLR_STEP_SPLIT_RANK_CLASSES) && src.max_rank > 64 &&
+                     (phase_mask & (VLR_PHASE_SHRINK_MMA | VLR_PHASE_EXPAND_MMA));
+  auto run = [&](bool expand, int cls, cudaStream_t st) -> int {
+    const int h_in = expand ? kMaxRank : shrink_h_in, h_out = expand ? expand_h_out : kMaxRank;
+    const int flags = expand ? VLR_ATMM_APPLY_SCALE : 0;
+    TileSource a = src;
+    a.item_counter = counters + (expand ? 32 : 0) + (cls == 2 ? 16 : 0);
+    if (cls == 1) {                                    // ranks <= 64
+      a.max_rank = 64;
+      a.skip_ranks_above = 64;
+    } else if (cls == 2) {                             // ranks above 64
+      a.skip_ranks_upto = 64;
+      a.wide_below_rank = 0;                           // wide stages are for small ranks
+    }
+    return atmm_launch(nullptr, nullptr, nullptr, scales, a, max_mma_tiles, T, h_in, h_out, 0, dtype, flags, st, n_problems);
+  };
+  SideStream* side = nullptr;
+  if (split) {
+    side = side_stream();
+    if (side == nullptr) return VLR_ERR_DRIVER;
+    if ((ce = cudaEventRecord(side->fork, s)) != cudaSuccess) return (int)ce;
+    if ((ce = cudaStreamWaitEvent(side->stream, side->fork, 0)) != cudaSuccess) return (int)ce;
+    if (phase_mask & VLR_PHASE_SHRINK_MMA) rc = run(false, 2, side->stream);
+    if (rc == VLR_OK && (phase_mask & VLR_PHASE_EXPAND_MMA)) rc = run(true, 2, side->stream);
+  }
+  auto join = [&]() -> int {                           // in any case: a capture or the caller's stream is never left forked
+    if (side == nullptr) return VLR_OK;
+    cudaError_t je = cudaEventRecord(side->join, side->stream);
+    if (je == cudaSuccess) je = cudaStreamWaitEvent(s, side->join, 0);
+    return je == cudaSuccess ? VLR_OK : (int)je;
+  };
+  if (rc != VLR_OK) {
+    join();
+    return rc;
+  }
+  const int cls = split ? 1 : 0;
   // shrink
-  src.item_counter = counters;
-  if (phase_mask & VLR_PHASE_SHRINK_MMA)
-    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, shrink_h_in, kMaxRank, 0,
-                     dtype, 0, s, n_problems);
-  if (rc != VLR_OK) return rc;
-  if (phase_mask & VLR_PHASE_SHRINK_GATHER)
+  if (phase_mask & VLR_PHASE_SHRINK_MMA) rc = run(false, cls, s);
+  if (rc == VLR_OK && (phase_mask & VLR_PHASE_SHRINK_GATHER))
     rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, shrink_h_in,
                             kMaxRank, VLR_LAYOUT_ROWS, dtype, s, n_problems);
-  if (rc != VLR_OK) return rc;
   // expand
-  src.item_counter = counters + 32;
-  if (phase_mask & VLR_PHASE_EXPAND_MMA)
-    rc = atmm_launch(nullptr, nullptr, nullptr, scales, src, max_mma_tiles, T, kMaxRank, expand_h_out, 0,
-                     dtype, VLR_ATMM_APPLY_SCALE, s, n_problems);
+  if (rc == VLR_OK && (phase_mask & VLR_PHASE_EXPAND_MMA)) rc = run(true, cls, s);
+  const int jrc = join();
   if (rc != VLR_OK) return rc;
+  if (jrc != VLR_OK) return jrc;
   if (phase_mask & VLR_PHASE_EXPAND_GATHER)
     rc = bgmv_gather_launch(nullptr, nullptr, nullptr, scales, g, max_gather_tiles, kMaxRank,
                             expand_h_out, VLR_LAYOUT_ROWS, dtype, s, n_problems);

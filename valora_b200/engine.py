@@ -29,7 +29,7 @@ class LoraStepEngine:
                  tile_m: int = 128, mma_min_rows: Optional[int] = None, gather_rows_per_tile: Optional[int] = None,
                  alloc_activations: bool = True, gather_path: str = "mma",
                  wide_gather: Optional[bool] = None, input_of: Optional[Sequence[int]] = None,
-                 share_pools_with: Optional["LoraStepEngine"] = None):
+                 share_pools_with: Optional["LoraStepEngine"] = None, split_rank_classes: bool = True):
         """input_of[p] = the projection whose activations projection p reads (itself by
         default).  q, k and v of a transformer layer read the same rows, as do gate and
         up (lora_unordered_batch_infer.py:946-965 passes one `input_embs` view to three
@@ -54,6 +54,7 @@ class LoraStepEngine:
             mma_min_rows = int(self.table["mma_min_rows"])
         self.gather_path = gather_path
         self.wide_gather = wide_gather
+        self.split_rank_classes = split_rank_classes
         if gather_rows_per_tile is None:
             gather_rows_per_tile = int(self.table["gather_rows_per_tile"]) if gather_path == "mma" else 8
         if gather_path == "simt" and gather_rows_per_tile > 8:
@@ -179,7 +180,10 @@ class LoraStepEngine:
             wide = ops.STEP_WIDE_GATHER_STAGES if min(self.ranks) < self._wide_below else 0
         else:
             wide = (ops.STEP_WIDE_GATHER_STAGES | ops.STEP_ALL_WIDE_GATHER_STAGES) if self.wide_gather else 0
-        return ops.STEP_GATHER_ON_TENSOR_CORES | wide
+        # adapters on both sides of rank 64 resident: one launch per rank class, each with the
+        # operand ring cut for its ranks (split_rank_classes=False keeps one launch per kernel)
+        split = ops.STEP_SPLIT_RANK_CLASSES if (self.split_rank_classes and min(self.ranks) <= 64 < max(self.ranks)) else 0
+        return ops.STEP_GATHER_ON_TENSOR_CORES | wide | split
 
     def phases(self):
         """(name, phase bit) of the kernel launches of one step, in order."""

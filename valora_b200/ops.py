@@ -23,6 +23,7 @@ PHASE_SHRINK_MMA, PHASE_SHRINK_GATHER, PHASE_EXPAND_MMA, PHASE_EXPAND_GATHER, PH
 STEP_GATHER_ON_TENSOR_CORES = 16
 STEP_WIDE_GATHER_STAGES = 32
 STEP_ALL_WIDE_GATHER_STAGES = 64
+STEP_SPLIT_RANK_CLASSES = 128
 
 
 _NVTX = os.environ.get("VLR_NVTX") == "1"
