@@ -218,7 +218,7 @@ def bench_atmm(layers: int, reps: int, warmup: int, dev, eager: bool = False):
 
 
 def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: bool = False, gather_rows: int = 0,
-               model: bool = False, graph: bool = False):
+               model: bool = False, graph: bool = False, ranks=None, split_rank_classes: bool = True):
     """A config through LoraStepEngine.step (device packer + one shrink and one
     expand launch): `layers` copies of the config's projections, every copy with its
     own pools and activations, CUDA events around each stage.  shared_x: q/k/v and
@@ -227,9 +227,15 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
     layer instead of the config's own single projection (a decode step of the whole
     model for config 1).  graph: the step is also captured into a CUDA graph and the
     replays are timed (`graph_ms_per_step`): what a serving loop that replays its
-    decode step pays, without the host's launch path between the kernels."""
+    decode step pays, without the host's launch path between the kernels.
+    ranks: every adapter's rank redrawn from this list (seed 7) - the same batch with
+    other ranks, e.g. [16] for the by-rank tables.  split_rank_classes=False: one launch per
+    kernel even with adapters on both sides of rank 64."""
     from .engine import LoraStepEngine
     b = workloads.CONFIGS[config]()
+    if ranks:
+        b.ranks = np.random.default_rng(7).choice(np.array(ranks), size=b.n_adapters).astype(np.int64)
+        b.name += "_ranks_" + "_".join(str(r) for r in ranks)
     if model:
         b.projections = list(workloads.PROJECTIONS)
         b.name += "_7proj"
@@ -240,6 +246,7 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
             raise SystemExit("--shared-x needs a config with the seven projections (2 or 3)")
         input_of = list(workloads.SHARED_INPUT_OF)
     eng = LoraStepEngine(b.projections, b.ranks, b.scalings(), b.dtype, dev, layers, b.T, input_of=input_of,
+                         split_rank_classes=split_rank_classes,
                          gather_rows_per_tile=gather_rows or None)
     eng.randomize_weights(seed=b.seed)
     g = torch.Generator(device=dev)
@@ -256,23 +263,22 @@ def bench_step(config: int, layers: int, reps: int, warmup: int, dev, shared_x: 
     counts = packed.host_counts()
     names = ["pack"] + [n for n, _ in eng.phases()]
     ms = {n: [] for n in names}
-    tot = []
+    # Two timings per repetition, interleaved so that both see the same clocks.  (1) stage by
+    # stage: one call per stage with events between them.  (2) the step itself: one call, nothing
+    # recorded between its launches - a step that runs its kernels once per rank class overlaps
+    # the two classes, which the per-stage calls cannot.
+    tot, whole = [], []
     for _ in range(reps):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
         eng.step_timed(tok, ev)
-        torch.cuda.synchronize()
-        for i, n in enumerate(names):
-            ms[n].append(ev[i].elapsed_time(ev[i + 1]))
-        tot.append(ev[0].elapsed_time(ev[-1]))
-    # the step itself: one call, nothing recorded between its launches (a step that runs its
-    # kernels once per rank class overlaps the two classes, which the per-phase calls above cannot)
-    whole = []
-    for _ in range(reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         eng.step(tok)
         e1.record()
         torch.cuda.synchronize()
+        for i, n in enumerate(names):
+            ms[n].append(ev[i].elapsed_time(ev[i + 1]))
+        tot.append(ev[0].elapsed_time(ev[-1]))
         whole.append(e0.elapsed_time(e1))
     if ops.device_status() != 0:
         raise SystemExit("a bounded wait gave up inside a kernel")
@@ -468,6 +474,9 @@ def main():
     ap.add_argument("--model", action="store_true",
                     help="step API: the batch over the seven model projections per layer instead of the config's own")
     ap.add_argument("--graph", action="store_true", help="step API: also time replays of the step from a CUDA graph")
+    ap.add_argument("--ranks", default="", help="step API: redraw every adapter's rank from this comma list (e.g. 16)")
+    ap.add_argument("--no-rank-split", action="store_true",
+                    help="step API: one launch per kernel even with adapters on both sides of rank 64")
     ap.add_argument("--trace", choices=["shrink", "expand"],
                     help="step API: print the stage timing of CTA 0 of one launch instead of timing steps")
     args = ap.parse_args()
@@ -487,7 +496,8 @@ def main():
     else:
         default_layers = {1: 32, 2: 4, 3: 32, 4: 8}[args.config]
         print(json.dumps(bench_step(args.config, args.layers or default_layers, args.reps, args.warmup, dev,
-                                    args.shared_x, args.gather_rows, args.model, args.graph)))
+                                    args.shared_x, args.gather_rows, args.model, args.graph,
+                                    [int(r) for r in args.ranks.split(",") if r], not args.no_rank_split)))
 
 
 if __name__ == "__main__":
