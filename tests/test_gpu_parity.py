@@ -198,8 +198,10 @@ def test_pack_configs(ops, cfg, sort):
 
 def test_pack_random_and_reference_offsets(ops):
     rng = np.random.default_rng(0)
-    # 16384 rows is the largest batch packed in shared memory; above it the workspace is used
-    for T, n in ((1000, 7), (5000, 300), (257, 2), (4097, 1024), (16384, 1024), (16385, 64), (40000, 2000)):
+    # 1024 rows is the largest batch packed by one launch, 16384 the largest whose tile pass works in
+    # shared memory; above that the workspace is used
+    for T, n in ((1000, 7), (5000, 300), (257, 2), (4097, 1024), (1024, 40), (1025, 40),
+                 (16384, 1024), (16385, 64), (40000, 2000)):
         ranks = rng.choice([8, 16, 32, 64, 128], size=n)
         # requests of random length, as the engine's repeat_interleave builds them
         req = rng.integers(0, n, size=T // 5 + 1)

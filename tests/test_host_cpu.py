@@ -156,3 +156,30 @@ def test_launcher_follows_the_tile_table():
     assert tile_table.choice(lib, bool(e0["step"]), e0["max_rank"])["shrink_stages"] == t["entries"][0]["shrink_stages"]
     eng = t["engine"]
     assert eng["gather_rows_per_tile"] <= 32 and eng["mma_min_rows"] >= 1
+
+
+def test_python_constants_mirror_the_header():
+    """The flag and layout values the Python layer passes are the header's `#define`s."""
+    import os
+    import re
+    from valora_b200 import ops
+    hdr = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "vlr.h")).read()
+    defs = {m.group(1): int(m.group(2), 0) for m in re.finditer(r"#define\s+(VLR_\w+)\s+(-?\d+)\b", hdr)}
+    pairs = {
+        "VLR_F16": ops.F16, "VLR_BF16": ops.BF16, "VLR_LAYOUT_PUNICA": ops.LAYOUT_PUNICA, "VLR_LAYOUT_ROWS": ops.LAYOUT_ROWS,
+        "VLR_ATMM_ACCUMULATE_SHRINK": ops.ATMM_ACCUMULATE_SHRINK, "VLR_ATMM_APPLY_SCALE": ops.ATMM_APPLY_SCALE,
+        "VLR_ATMM_FULL_TILES": ops.ATMM_FULL_TILES, "VLR_TILE_INTS": ops.TILE_INTS, "VLR_COUNT_INTS": ops.COUNT_INTS,
+        "VLR_PHASE_SHRINK_MMA": ops.PHASE_SHRINK_MMA, "VLR_PHASE_SHRINK_GATHER": ops.PHASE_SHRINK_GATHER,
+        "VLR_PHASE_EXPAND_MMA": ops.PHASE_EXPAND_MMA, "VLR_PHASE_EXPAND_GATHER": ops.PHASE_EXPAND_GATHER,
+        "VLR_STEP_GATHER_ON_TENSOR_CORES": ops.STEP_GATHER_ON_TENSOR_CORES,
+        "VLR_STEP_WIDE_GATHER_STAGES": ops.STEP_WIDE_GATHER_STAGES,
+        "VLR_STEP_ALL_WIDE_GATHER_STAGES": ops.STEP_ALL_WIDE_GATHER_STAGES,
+        "VLR_STEP_SPLIT_RANK_CLASSES": ops.STEP_SPLIT_RANK_CLASSES,
+    }
+    for name, val in pairs.items():
+        assert name in defs, name
+        assert defs[name] == val, name
+    # the step's flags are distinct bits above the four phase bits
+    bits = [ops.STEP_GATHER_ON_TENSOR_CORES, ops.STEP_WIDE_GATHER_STAGES, ops.STEP_ALL_WIDE_GATHER_STAGES,
+            ops.STEP_SPLIT_RANK_CLASSES]
+    assert len(set(bits)) == 4 and all(b & ops.PHASE_ALL == 0 and b & (b - 1) == 0 for b in bits)

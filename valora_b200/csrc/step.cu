@@ -16,6 +16,8 @@ namespace {
 struct SideStream {
   cudaStream_t stream;
   cudaEvent_t fork, join;
+  std::mutex pair;      // a record and the wait on it are one step for concurrent callers: the wait
+                        // takes the event's latest record
 };
 SideStream* side_stream() {
   constexpr int kMaxDev = 64;
@@ -26,11 +28,10 @@ SideStream* side_stream() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
   if (!made[dev]) {
-    SideStream ss{};
+    SideStream& ss = slots[dev];
     if (cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&ss.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&ss.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
-    slots[dev] = ss;
     made[dev] = true;
   }
   return &slots[dev];
@@ -160,13 +161,17 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   if (split) {
     side = side_stream();
     if (side == nullptr) return VLR_ERR_DRIVER;
-    if ((ce = cudaEventRecord(side->fork, s)) != cudaSuccess) return (int)ce;
-    if ((ce = cudaStreamWaitEvent(side->stream, side->fork, 0)) != cudaSuccess) return (int)ce;
+    {
+      std::lock_guard<std::mutex> lock(side->pair);
+      if ((ce = cudaEventRecord(side->fork, s)) != cudaSuccess) return (int)ce;
+      if ((ce = cudaStreamWaitEvent(side->stream, side->fork, 0)) != cudaSuccess) return (int)ce;
+    }
     if (phase_mask & VLR_PHASE_SHRINK_MMA) rc = run(false, 2, side->stream);
     if (rc == VLR_OK && (phase_mask & VLR_PHASE_EXPAND_MMA)) rc = run(true, 2, side->stream);
   }
   auto join = [&]() -> int {                           // in any case: a capture or the caller's stream is never left forked
     if (side == nullptr) return VLR_OK;
+    std::lock_guard<std::mutex> lock(side->pair);
     cudaError_t je = cudaEventRecord(side->join, side->stream);
     if (je == cudaSuccess) je = cudaStreamWaitEvent(s, side->join, 0);
     return je == cudaSuccess ? VLR_OK : (int)je;
