@@ -292,7 +292,8 @@ typedef struct {
 size_t vlr_step_plan_bytes(int n_problems);
 int vlr_step_plan_build(const vlr_problem_t* problems, int n_problems, int64_t max_rows, int dtype,
                         void* plan_host);
-/* workspace: the shrink results, n_problems * T * 128 elements */
+/* workspace: the shrink results (n_problems * T * 128 elements), the work-item counters and
+ * the tile lists of the two rank classes (16 T bytes) */
 size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
 /*
  * plan_dev: device copy of the plan.  tiles / gather_rows / counts: device
@@ -336,7 +337,9 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
  * once over the tiles of adapters of rank <= 64 and once over the others, so that the first
  * launch cuts its 192 KB operand ring for those ranks (four stages) instead of for the
  * largest rank of the step (three): in a batch of mixed ranks the tiles up to rank 64 ran
- * 18-34 % slower on the three-stage ring.  Set it when adapters of both classes are
+ * 18-34 % slower on the three-stage ring.  A small kernel ahead of them lists each class's
+ * tiles in the workspace; the second class runs on a library-owned side stream, forked from
+ * and joined to `stream` inside the call.  Set it when adapters of both classes are
  * resident; same results bit for bit. */
 #define VLR_STEP_SPLIT_RANK_CLASSES 128
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,

@@ -1088,22 +1088,32 @@ def test_rank_class_split_changes_nothing(ops):
     b4 = workloads.config4(n_gpus=8, rank=5)
     assert min(b4.ranks) <= 64 < max(b4.ranks)
     tok = torch.from_numpy(b4.tok_adapter.astype(np.int64)).to(DEV)
-    outs = []
-    for split in (True, False):
-        eng = LoraStepEngine([("p", 1024, 512), ("q", 512, 1024)], b4.ranks, b4.scalings(), dtype, DEV, 2, b4.T,
-                             split_rank_classes=split)
-        assert bool(eng._gather_flag() & ops.STEP_SPLIT_RANK_CLASSES) == split
-        eng.randomize_weights(seed=71)
-        gg = torch.Generator(device=DEV)
-        gg.manual_seed(72)
-        for l in range(2):
-            for p in range(2):
-                eng.x[l][p].normal_(generator=gg)
-                eng.y[l][p].normal_(generator=gg)
-        eng.step(tok)
-        torch.cuda.synchronize()
-        assert ops.device_status() == 0
-        outs.append([eng.y[l][p].cpu() for l in range(2) for p in range(2)])
-        del eng
-    for a, b in zip(*outs):
-        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # second case: the only adapter above rank 64 is resident but not in the batch - the launches of
+    # that class find no tile
+    unused = sorted(set(range(len(b4.ranks))) - set(np.unique(b4.tok_adapter).tolist()))
+    assert unused
+    lone = np.minimum(b4.ranks, 64)
+    lone[unused[0]] = 128
+    for ranks in (b4.ranks, lone):
+        scal = (workloads.ALPHA / ranks).astype(np.float32)
+        outs = []
+        for split in (True, False):
+            eng = LoraStepEngine([("p", 1024, 512), ("q", 512, 1024)], ranks, scal, dtype, DEV, 2, b4.T,
+                                 split_rank_classes=split)
+            assert bool(eng._gather_flag() & ops.STEP_SPLIT_RANK_CLASSES) == split
+            eng.randomize_weights(seed=71)
+            gg = torch.Generator(device=DEV)
+            gg.manual_seed(72)
+            for l in range(2):
+                for p in range(2):
+                    eng.x[l][p].normal_(generator=gg)
+                    eng.y[l][p].normal_(generator=gg)
+            y0 = eng.y[1][1].clone()
+            eng.step(tok)
+            torch.cuda.synchronize()
+            assert ops.device_status() == 0
+            assert not torch.equal(y0, eng.y[1][1])
+            outs.append([eng.y[l][p].cpu() for l in range(2) for p in range(2)])
+            del eng
+        for a, b in zip(*outs):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16))

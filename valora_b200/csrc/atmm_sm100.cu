@@ -121,9 +121,11 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
   ti.split = (int)(item % src.nsplit);
   const int64_t tb = item / src.nsplit;
   if (src.mode == 1) {
-    const int n_tiles = src.counts[VLR_COUNT_MMA_TILES] +
-                        (src.gather_mma ? src.counts[VLR_COUNT_GATHER_TILES] : 0);
-    const int b = (int)(tb % n_tiles);
+    const int n_tiles = src.class_list != nullptr
+                            ? *src.class_count
+                            : src.counts[VLR_COUNT_MMA_TILES] + (src.gather_mma ? src.counts[VLR_COUNT_GATHER_TILES] : 0);
+    int b = (int)(tb % n_tiles);
+    if (src.class_list != nullptr) b = src.class_list[b];
     ti.problem = (int)(tb / n_tiles);
     const int32_t* t = src.tiles + (int64_t)b * VLR_TILE_INTS;
     ti.valid = 1;
@@ -132,12 +134,6 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
     ti.rank = t[2];
     ti.row0 = t[3];
     ti.rows = t[4];
-    if (ti.rank > 0 && ti.rank <= kMaxRank &&
-        ((src.skip_ranks_upto > 0 && ti.rank <= src.skip_ranks_upto) ||
-         (src.skip_ranks_above > 0 && ti.rank > src.skip_ranks_above))) {
-      ti.valid = 2;                  // the other rank class's launch takes this tile
-      return ti;
-    }
   } else {
     const int b = (int)tb;
     const int tm = (!expand && src.tile_rows > 0) ? src.tile_rows : kTileM;
@@ -191,6 +187,7 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
 }
 
 __device__ __forceinline__ int64_t total_items(const TileSource& src) {
+  if (src.mode == 1 && src.class_list != nullptr) return (int64_t)*src.class_count * src.n_problems * src.nsplit;
   if (src.mode == 1)
     return (int64_t)(src.counts[VLR_COUNT_MMA_TILES] +
                      (src.gather_mma ? src.counts[VLR_COUNT_GATHER_TILES] : 0)) *
@@ -258,25 +255,20 @@ __device__ __forceinline__ void feed_tiles(const TileSource& src, const ItemFeed
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (!ok) return;
     long long item = 0;
+    if (lane == 0) {
+      if (src.item_counter == nullptr) item = (long long)blockIdx.x + (long long)k * gridDim.x;
+      else item = k == 0 ? (long long)blockIdx.x
+                         : (long long)gridDim.x + (long long)atomicAdd(src.item_counter, 1u);
+      if (item >= total) item = -1;
+    }
+    item = __shfl_sync(0xffffffffu, item, 0);
     TileInfo ti;
-    bool first = k == 0;
-    do {                                               // tiles of the other rank class are drawn and dropped
-      if (lane == 0) {
-        if (src.item_counter == nullptr) item = (long long)blockIdx.x + (long long)k * gridDim.x;
-        else item = first ? (long long)blockIdx.x
-                          : (long long)gridDim.x + (long long)atomicAdd(src.item_counter, 1u);
-        if (item >= total) item = -1;
-      }
-      first = false;
-      item = __shfl_sync(0xffffffffu, item, 0);
-      ti.valid = -1;
-      ti.gather = 0;
-      ti.rows = 0;
-      ti.row0 = 0;
-      ti.problem = 0;
-      if (item >= 0) ti = get_tile(src, item, expand);
-    } while (ti.valid == 2 && src.item_counter != nullptr);
-    if (ti.valid == 2) ti.valid = 0;
+    ti.valid = -1;
+    ti.gather = 0;
+    ti.rows = 0;
+    ti.row0 = 0;
+    ti.problem = 0;
+    if (item >= 0) ti = get_tile(src, item, expand);
     int h = h_arg;
     const void* yb = y_arg;
     int g = 0;

@@ -79,9 +79,11 @@ struct TileSource {
                                      // caller presets 0 (none), 1 (the tile table's threshold) or -1 (all tiles);
                                      // the launcher resolves it
   // A step may run a kernel twice, once per rank class, so that each launch cuts its operand
-  // ring for the ranks it meets: tiles of a (valid) rank <= skip_ranks_upto, or > skip_ranks_above,
-  // belong to the other launch and are passed over silently.  0 = no such bound.
-  int skip_ranks_upto, skip_ranks_above;
+  // ring for the ranks it meets.  A launch of a class works on class_list[0 .. *class_count):
+  // the indices of its tiles in `tiles`, in order (written on the device ahead of the
+  // launches).  null = every tile.
+  const int32_t* class_list;
+  const int32_t* class_count;
   // adapter tables
   const int64_t* a_start;
   const int64_t* a_loc;

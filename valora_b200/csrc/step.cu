@@ -36,6 +36,44 @@ SideStream* side_stream() {
   }
   return &slots[dev];
 }
+
+// The step's tiles by rank class: indices of the tiles of rank <= split_rank in list1, of the others
+// in list2, each in the order of `tiles`; the two counts in cls_count[0], cls_count[16] (64 bytes
+// apart).  One CTA; n is a few thousand at most.
+__global__ void __launch_bounds__(1024)
+classify_tiles_kernel(const int32_t* __restrict__ tiles, const int32_t* __restrict__ counts, int gather_mma,
+                      int split_rank, int cap, int32_t* cls_count, int32_t* list1, int32_t* list2) {
+  __shared__ int w1[32], w2[32];
+  __shared__ int base1_s, base2_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int n = counts[VLR_COUNT_MMA_TILES] + (gather_mma ? counts[VLR_COUNT_GATHER_TILES] : 0);
+  n = n < cap ? n : cap;
+  if (tid == 0) { base1_s = 0; base2_s = 0; }
+  __syncthreads();
+  for (int b0 = 0; b0 < n; b0 += 1024) {
+    const int b = b0 + tid;
+    const bool in = b < n;
+    const bool c2 = in && tiles[(int64_t)b * VLR_TILE_INTS + 2] > split_rank;
+    const bool c1 = in && !c2;
+    const unsigned m1 = __ballot_sync(0xffffffffu, c1), m2 = __ballot_sync(0xffffffffu, c2);
+    if (lane == 0) { w1[warp] = __popc(m1); w2[warp] = __popc(m2); }
+    __syncthreads();
+    int o1 = base1_s, o2 = base2_s;                   // offsets of this warp: the warps before it
+    for (int w = 0; w < warp; ++w) { o1 += w1[w]; o2 += w2[w]; }
+    const unsigned below = (1u << lane) - 1u;
+    if (c1) list1[o1 + __popc(m1 & below)] = b;
+    if (c2) list2[o2 + __popc(m2 & below)] = b;
+    __syncthreads();
+    if (tid == 0) {
+      int t1 = 0, t2 = 0;
+      for (int w = 0; w < 32; ++w) { t1 += w1[w]; t2 += w2[w]; }
+      base1_s += t1;
+      base2_s += t2;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) { cls_count[0] = base1_s; cls_count[16] = base2_s; }
+}
 }  // namespace
 
 extern "C" size_t vlr_step_plan_bytes(int n_problems) {
@@ -75,7 +113,8 @@ extern "C" int vlr_step_plan_build(const vlr_problem_t* problems, int n_problems
 
 extern "C" size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems) {
   if (T <= 0 || n_problems <= 0) return 256;
-  return (size_t)n_problems * (size_t)T * kMaxRank * 2 + 256 + 512;   // V buffers, alignment, work-item counters
+  // V buffers, alignment, work-item counters; the two rank classes' counts and tile lists (2 T entries each)
+  return (size_t)n_problems * (size_t)T * kMaxRank * 2 + 256 + 512 + 256 + (size_t)T * 16;
 }
 
 extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
@@ -91,9 +130,13 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   if ((reinterpret_cast<uintptr_t>(plan_dev) & 127u) != 0) return VLR_ERR_ALIGN;
   char* vb = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~uintptr_t(255));
   const size_t need = (size_t)n_problems * (size_t)T * kMaxRank * 2;
-  const size_t need_all = ((need + 255) & ~size_t(255)) + 256;     // + four work-item counters, 64 bytes apart
+  // + four work-item counters, 64 bytes apart; + class counts and the two class lists
+  const size_t need_all = ((need + 255) & ~size_t(255)) + 256 + 256 + (size_t)T * 16;
   if ((size_t)(vb - reinterpret_cast<char*>(workspace)) + need_all > workspace_bytes) return VLR_ERR_WORKSPACE;
   unsigned int* counters = reinterpret_cast<unsigned int*>(vb + ((need + 255) & ~size_t(255)));
+  int32_t* cls_count = reinterpret_cast<int32_t*>(counters + 64);
+  int32_t* cls_list1 = cls_count + 64;
+  int32_t* cls_list2 = cls_list1 + 2 * T;
   // every tile holds at least one row
   if (max_mma_tiles <= 0 || max_mma_tiles > T) max_mma_tiles = T;
   if (max_gather_tiles <= 0 || max_gather_tiles > T) max_gather_tiles = T;
@@ -150,9 +193,11 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
     a.item_counter = counters + (expand ? 32 : 0) + (cls == 2 ? 16 : 0);
     if (cls == 1) {                                    // ranks <= 64
       a.max_rank = 64;
-      a.skip_ranks_above = 64;
+      a.class_list = cls_list1;
+      a.class_count = cls_count;
     } else if (cls == 2) {                             // ranks above 64
-      a.skip_ranks_upto = 64;
+      a.class_list = cls_list2;
+      a.class_count = cls_count + 16;
       a.wide_below_rank = 0;                           // wide stages are for small ranks
     }
     return atmm_launch(nullptr, nullptr, nullptr, scales, a, max_mma_tiles, T, h_in, h_out, 0, dtype, flags, st, n_problems);
@@ -161,6 +206,10 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   if (split) {
     side = side_stream();
     if (side == nullptr) return VLR_ERR_DRIVER;
+    // which tiles belong to which class (a rank the kernels do not support lands in one of the two
+    // and is reported by that launch)
+    classify_tiles_kernel<<<1, 1024, 0, s>>>(tiles, counts, src.gather_mma, 64, (int)(2 * T), cls_count, cls_list1, cls_list2);
+    if ((rc = launch_status()) != VLR_OK) return rc;
     {
       std::lock_guard<std::mutex> lock(side->pair);
       if ((ce = cudaEventRecord(side->fork, s)) != cudaSuccess) return (int)ce;
