@@ -1117,3 +1117,27 @@ def test_rank_class_split_changes_nothing(ops):
             del eng
         for a, b in zip(*outs):
             assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_step_random_ranks_widths_and_lengths(ops, seed):
+    """Seeded random batches on the step: every rank the kernels take (multiples of 8 up to 128,
+    so rank % 16 == 8 as well, on both sides of the rank-class split), widths whose K blocks do
+    not fill the last stage of a gather tile (9, 13, 17 blocks), requests of 1 .. 200 tokens in
+    random order, so that a segment mixes consecutive-row tiles, short chunks and single rows,
+    and gather tiles of 1 .. 32 rows occur."""
+    rng = np.random.default_rng(1000 + seed)
+    n_ad = 24
+    ranks = rng.choice(np.arange(8, 129, 8), size=n_ad).astype(np.int64)
+    ranks[:4] = [8, 24, 72, 128]
+    n_req = 90
+    req_ad = rng.integers(0, n_ad, size=n_req).astype(np.int32)
+    req_len = np.where(rng.random(n_req) < 0.7, 1, rng.integers(2, 200, size=n_req)).astype(np.int64)
+    # a popular adapter with many decode rows: gather tiles of 32 rows and a remainder
+    req_ad[:45] = np.where(rng.random(45) < 0.8, 3, req_ad[:45])
+    tok = np.repeat(req_ad, req_len).astype(np.int32)
+    widths = [(576, 832), (1088, 576), (832, 1088)][seed]
+    b = workloads.Batch(f"random_{seed}", [torch.bfloat16, torch.float16, torch.bfloat16][seed], ranks, tok, req_ad,
+                        req_len, int((req_len > 1).sum()), [("p", widths[0], widths[1]), ("q", widths[1], widths[0])],
+                        seed=2000 + seed)
+    _step_case(ops, b, [0, 1], layers=2)
