@@ -125,15 +125,18 @@ __device__ __forceinline__ TileInfo get_tile(const TileSource& src, int64_t item
                             ? *src.class_count
                             : src.counts[VLR_COUNT_MMA_TILES] + (src.gather_mma ? src.counts[VLR_COUNT_GATHER_TILES] : 0);
     int b = (int)(tb % n_tiles);
-    if (src.class_list != nullptr) b = src.class_list[b];
+    if (src.class_list != nullptr) b = __ldg(src.class_list + b);
     ti.problem = (int)(tb / n_tiles);
+    // the records are the same for every problem of the step: read-only path, so that after a
+    // CTA's first problem they come from L1
     const int32_t* t = src.tiles + (int64_t)b * VLR_TILE_INTS;
+    const int4 r0 = __ldg(reinterpret_cast<const int4*>(t));
     ti.valid = 1;
-    ti.gather = t[0] == VLR_TILE_GATHER;
-    ti.adapter = t[1];
-    ti.rank = t[2];
-    ti.row0 = t[3];
-    ti.rows = t[4];
+    ti.gather = r0.x == VLR_TILE_GATHER;
+    ti.adapter = r0.y;
+    ti.rank = r0.z;
+    ti.row0 = r0.w;
+    ti.rows = __ldg(t + 4);
   } else {
     const int b = (int)tb;
     const int tm = (!expand && src.tile_rows > 0) ? src.tile_rows : kTileM;
@@ -206,6 +209,7 @@ __device__ __forceinline__ int64_t total_items(const TileSource& src) {
 // warp reads the ring in order, so all roles see the same sequence and none of them waits
 // for global memory at an item boundary.
 constexpr int kItemRing = 2;
+constexpr int kItemSlotBytes = 1024;                   // shared memory for the ring's slots
 struct ItemSlot {
   TileInfo ti;                                         // ti.valid: 1 work, 0 skip, -1 end of the sequence
   int h;                                               // shrink: the problem's h_in; expand: its h_out
@@ -213,6 +217,7 @@ struct ItemSlot {
   const void* ybase;                                   // expand: the problem's Y
   int grow[kGatherRows];                               // rows of a gather tile
 };
+static_assert(sizeof(ItemSlot) * kItemRing <= kItemSlotBytes, "item slots outgrow their shared memory");
 struct ItemFeed {
   uint32_t full0, empty0;                              // shared-memory addresses of the barriers
   ItemSlot* slots;
@@ -248,6 +253,9 @@ __device__ __forceinline__ void feed_tiles(const TileSource& src, const ItemFeed
                                            bool expand, int h_arg, const void* y_arg,
                                            volatile int* abort_flag) {
   const int lane = threadIdx.x & 31;
+  // (A ring of four slots and drawing the next item one iteration ahead of its use were measured:
+  // a CTA then sits on more undistributed items at the end of a launch - config 2's expand 1.25 ->
+  // 1.41 ms, config 3 +3 % - and batches of small tiles gained nothing.)
   for (uint32_t k = 0;; ++k) {
     const uint32_t s = k % kItemRing;
     bool ok = true;
@@ -321,7 +329,7 @@ constexpr int kShrinkMaxSub = 16;                      // K blocks per stage, at
 // The A operand of an MMA is a window of 128 rows (16 KB) from where a block's
 // activation rows start, whatever was loaded there: the window of the ring's last
 // block runs past the ring, so that much shared memory is allocated behind it.
-constexpr int kShrinkSmem = 1024 + kRingBytes + 512 + 512 + kTileM * 128;   // + barriers, item slots, window slack
+constexpr int kShrinkSmem = 1024 + kRingBytes + 512 + kItemSlotBytes + kTileM * 128;   // + barriers, item slots, window slack
 
 // A stage holds as many K blocks as fit: a block = the tile's activation rows
 // (2 KB for gathered rows, 4..16 KB for consecutive ones) then the adapter's rank
@@ -742,7 +750,7 @@ constexpr int kExpABytes = 2 * kTileM * 128;           // V tile, two 64-column 
 // rank 128, 32 + 8 KB for a 256-column gather tile.  Launches that cannot meet a rank
 // above 64 run four 48 KB stages, the others three 64 KB stages.
 constexpr int kExpAccBufs = 4;                         // accumulators of 128 TMEM columns
-constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512 + 512;      // + barriers, item slots
+constexpr int kExpSmem = 1024 + kExpABytes + kRingBytes + 512 + kItemSlotBytes;      // + barriers, item slots
 
 // A work item's output tiles.  Consecutive-row tiles use 128 columns per stage
 // (B 64-column blocks 16 KB apart).  Gather tiles stream almost only weights, so

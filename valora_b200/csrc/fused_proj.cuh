@@ -24,7 +24,7 @@ constexpr int kFpStageBytes = 48 * 1024;
 constexpr int kFpTileN = 256;
 constexpr int kFpWBlock = 64 * 128;                    // one [64 x 64] box of W: 8 KB
 constexpr int kFpOutBytes = kExpEpiWarps * 32 * 128;   // per-warp staging [32 rows x 64 columns]
-constexpr int kFpSmem = 1024 + kExpABytes + kFpStages * kFpStageBytes + kFpOutBytes + 512 + 512;
+constexpr int kFpSmem = 1024 + kExpABytes + kFpStages * kFpStageBytes + kFpOutBytes + 512 + kItemSlotBytes;
 
 struct FusedArgs {
   const void* v;            // V' [T, v_pitch], scaled shrink result
