@@ -99,6 +99,21 @@ __device__ __forceinline__ void load_w_rows(uint32_t dst, const MapSet* ms, int 
   }
 }
 
+// The gather form of the shrink: n_pad consecutive pool cells x g K blocks as at most four 3-D
+// boxes; cell c's blocks land as the lines (c * g + j), j < g, behind one another.
+__device__ __forceinline__ void load_w3_rows(uint32_t dst, const MapSet* ms, int gsel, int g, int kb0, int row0,
+                                             int n_pad, uint32_t bar) {
+  int done = 0;
+#pragma unroll
+  for (int b = 3; b >= 0; --b) {
+    const int h = 16 << b;
+    if (h * g <= 256 && n_pad - done >= h) {
+      tma_load_3d(dst + (uint32_t)(done * g) * 128u, &ms->w3[gsel][b], 0, kb0, row0 + done, bar);
+      done += h;
+    }
+  }
+}
+
 // Device-side status: bit 0 (1) a bounded wait gave up and the kernel returned early, bit 1
 // (2) a tile record was outside what the launch supports (rank above the launch's bound or not
 // a multiple of 8, more rows than a tile holds) and was skipped.  A step may name its own
@@ -348,27 +363,49 @@ __device__ __forceinline__ SubLayout sub_layout(const TileInfo& ti, int n_pad, u
 // fetched g K blocks at a time with ONE copy (a [1 row x g blocks x 64 columns] box of the 3-D
 // view of the activations), which lands as g consecutive 128-byte lines.  Token i then owns
 // the lines i*g .. i*g+g-1 of the stage's X region, line i*g+j holding its K block j.  The
-// stage's g weight blocks lie one behind the other, so they form ONE operand of g * n_pad
-// rows, and one MMA per 16-column K slice multiplies the whole X region with all of them:
-// accumulator columns j*n_pad .. j*n_pad+n_pad-1 pair every line with the weights of K block
-// j.  Of those only the lines L with L % g == j mean anything (the others paired a token's
-// block with another block's weights); the epilogue picks them and adds the g of them that
-// belong to a token.  One sixteenth to a quarter of the copy instructions of one-row,
-// one-block copies, and four MMAs per stage instead of 4 g: at 60-80 cycles per MMA for
-// the issuing thread, 256 narrow MMAs per tile had been what bounded these tiles below rank 128.
+// adapter's weights come the same way, as [cells x g blocks x 64 columns] boxes of the pool: rank
+// row c's K block j is line c*g+j of the W region, so every weight row is read in pieces of
+// g * 128 contiguous bytes (with one [cells x 64 columns] box per K block they were 128-byte
+// pieces 8 KB apart, and a stage of such pieces took about 6000 cycles to land).  The W region
+// is ONE K-major operand of n_pad*g rows, and one MMA per 16-column K slice (M = 128 lines,
+// N = n_pad*g <= 256) multiplies the whole X region with it: accumulator column c*g+j pairs
+// every line with rank row c of K block j.  Of those only the lines L with L % g == j mean
+// anything (the others paired a token's block with another block's weights); the epilogue picks
+// them and adds the g of them that belong to a token.  Four MMAs per stage instead of 4 g: at
+// 60-80 cycles per MMA for the issuing thread, 256 narrow MMAs per tile had been what bounded
+// these tiles below rank 128.
 //   g = 8 K blocks per stage (rank <= 32), 4 (rank <= 64), 2 above - and no more than the 128
 //   lines of the operand allow: 8 for tiles of up to 16 rows, else 4
-// Stage: [X region, cap * g lines][weights of block 0] .. [weights of block g-1]
-struct GatherLayout { int g, gsel, astr; uint32_t xbytes, wbytes; };
+// Stage: [X region, cap * g lines][W region, n_pad * g lines]
+struct GatherLayout { int g, gsel; uint32_t xbytes, wbytes; };
 __device__ __forceinline__ GatherLayout gather_layout(int n_pad, int rows) {
   GatherLayout gl;
   const int cap = gather_cap(rows);
   gl.g = min(n_pad <= 32 ? 8 : (n_pad <= 64 ? 4 : 2), kTileM / cap);
-  gl.astr = n_pad;                                     // accumulator columns per K block
   gl.gsel = gl.g == 8 ? 2 : (gl.g == 4 ? 1 : 0);
   gl.xbytes = (uint32_t)(cap * gl.g) * 128u;
-  gl.wbytes = (uint32_t)n_pad * 128u;
+  gl.wbytes = (uint32_t)(n_pad * gl.g) * 128u;        // the whole W region
   return gl;
+}
+// Epilogue of such a tile: the 16 rank rows c0 .. c0+15 of this lane's line, which holds K block
+// jj: accumulator columns (c0 + c) * G + jj.  G loads of 16 consecutive columns, each covering
+// 16 / G rank rows with all their blocks.
+template <int G>
+__device__ __forceinline__ void gather_collect(uint32_t tcol0, int jj, uint32_t (&r)[16]) {
+  constexpr int kPer = 16 / G;
+#pragma unroll
+  for (int a = 0; a < G; ++a) {
+    uint32_t p[16];
+    ptx::tmem_ld_32x16(tcol0 + (uint32_t)(a * 16), p);
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) {
+      uint32_t v = p[k * G];
+#pragma unroll
+      for (int j = 1; j < G; ++j) v = (jj == j) ? p[k * G + j] : v;
+      r[a * kPer + k] = v;
+    }
+  }
 }
 constexpr int kGather3MinBlocks = 8;                   // K blocks an activation row must have for this form
 
@@ -462,16 +499,13 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
           if ((int)(kiter % nprod) != warp) continue;
           const int s = kiter % nst;
           const int kb0 = st * gl.g;
-          const int nsub = min(gl.g, kblocks - kb0);
           if (lane == 0) {
             ok = mbar_wait(empty_bar(s), ((kiter / nst) & 1) ^ 1, &abort_s);
             if (ok) {
               trace_stamp(src, kiter, 0);
               // a box counts its full size, also where it reaches past the last K block (zero fill)
-              mbar_expect_tx(full_bar(s), (uint32_t)ti.rows * (uint32_t)gl.g * 128u + (uint32_t)nsub * gl.wbytes);
-              for (int j = 0; j < nsub; ++j)
-                load_w_rows(x_stage(s) + gl.xbytes + j * gl.wbytes, ms, (kb0 + j) * kBoxCols, (int)ti.wrow0, n_pad,
-                            full_bar(s));
+              mbar_expect_tx(full_bar(s), (uint32_t)ti.rows * (uint32_t)gl.g * 128u + gl.wbytes);
+              load_w3_rows(x_stage(s) + gl.xbytes, ms, gl.gsel, gl.g, kb0, (int)ti.wrow0, n_pad, full_bar(s));
               trace_stamp(src, kiter, 3);
             }
           }
@@ -546,34 +580,29 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
         ok = mbar_wait(tempty_bar(ab), ((li >> 1) & 1) ^ 1, &abort_s);
         if (ok) tc_fence_after();
         if (ti.gather && kblocks >= kGather3MinBlocks) {
-          // one MMA per K slice: the whole X region against the stage's weight blocks (N = nsub * n_pad)
+          // one MMA per K slice: the whole X region against the stage's W region (N = n_pad * g;
+          // K blocks past the activations' width arrive as zeros on both sides)
           const GatherLayout gl = gather_layout(n_pad, ti.rows);
           const int nstages = (kblocks + gl.g - 1) / gl.g;
           const bool bf = std::is_same<T, __nv_bfloat16>::value;
-          const uint32_t idesc_full = instr_desc_f16(bf, gl.g * n_pad, 0);
+          const int n_all = n_pad * gl.g;
+          // above rank 64 (g = 2) as two MMAs of half the rank rows each: measured 6 % faster than one of N = 256
+          const int n_mma = n_pad <= 64 ? n_all : n_all / 2;
+          const uint32_t idesc_g = instr_desc_f16(bf, n_mma, 0);
           for (int st = 0; st < nstages && ok; ++st, ++kiter) {
             const int s = kiter % nst;
             ok = mbar_wait(full_bar(s), (kiter / nst) & 1, &abort_s);
             if (!ok) break;
             trace_stamp(src, kiter, 1);
             tc_fence_after();
-            const int nsub = min(gl.g, kblocks - st * gl.g);
-            const uint32_t idesc_g = nsub == gl.g ? idesc_full : instr_desc_f16(bf, nsub * n_pad, 0);
             const uint64_t ad = smem_desc_sw128(x_stage(s), 16, 1024);
             const uint64_t bd = smem_desc_sw128(x_stage(s) + gl.xbytes, 16, 1024);
-            if (n_pad <= 64) {
+            for (int hN = 0; hN < n_all; hN += n_mma) {
+              const uint64_t bh = bd + (uint64_t)((hN * 128) >> 4);
 #pragma unroll
               for (int k = 0; k < kBoxCols / 16; ++k)
-                umma_f16(tacc, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), idesc_g, (st > 0 || k > 0) ? 1u : 0u);
-            } else {
-              // two blocks of 80 .. 128 rows: an MMA each measured 6 % faster than one of N = 256
-              for (int j = 0; j < nsub; ++j) {
-                const uint64_t bj = bd + (uint64_t)j * (uint64_t)(gl.wbytes >> 4);
-#pragma unroll
-                for (int k = 0; k < kBoxCols / 16; ++k)
-                  umma_f16(tacc + (uint32_t)(j * gl.astr), ad + (uint64_t)(2 * k), bj + (uint64_t)(2 * k), idesc,
-                           (st > 0 || k > 0) ? 1u : 0u);
-              }
+                umma_f16(tacc + (uint32_t)hN, ad + (uint64_t)(2 * k), bh + (uint64_t)(2 * k), idesc_g,
+                         (st > 0 || k > 0) ? 1u : 0u);
             }
             umma_commit(empty_bar(s));
             trace_stamp(src, kiter, 2);
@@ -670,17 +699,10 @@ atmm_shrink_kernel(const __grid_constant__ MapSet maps_,
           T* vrow = v + (int64_t)(tok < ti.rows ? my_row : 0) * v_pitch;
           for (int c = 0; c < n_pad; c += 16) {
             uint32_t r[16];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) r[e] = 0u;
-            for (int a = 0; a < gl.g; ++a) {
-              uint32_t p[16];
-              tmem_ld_32x16(tbuf + a * gl.astr + c, p);
-              tmem_ld_wait();
-              if (a == jj) {
-#pragma unroll
-                for (int e = 0; e < 16; ++e) r[e] = p[e];
-              }
-            }
+            const uint32_t tcol0 = tbuf + (uint32_t)(c * gl.g);
+            if (gl.g == 8) gather_collect<8>(tcol0, jj, r);
+            else if (gl.g == 4) gather_collect<4>(tcol0, jj, r);
+            else gather_collect<2>(tcol0, jj, r);
             for (int o = 1; o < gl.g; o <<= 1) {
 #pragma unroll
               for (int e = 0; e < 16; ++e)
@@ -1263,12 +1285,13 @@ int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int6
 
 // [rows][cols / 64][64] view of a row-major [rows, cols] tensor (cols % 64 == 0), box = one
 // row x kblocks consecutive 64-column blocks
-static int make_map_row3(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int kblocks) {
+static int make_map_row3(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int kblocks,
+                         int box_rows = 1) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return VLR_ERR_DRIVER;
   cuuint64_t dims[3] = {(cuuint64_t)kBoxCols, (cuuint64_t)(cols / kBoxCols), (cuuint64_t)rows};
   cuuint64_t strides[2] = {(cuuint64_t)kBoxCols * 2, (cuuint64_t)cols * 2};
-  cuuint32_t box[3] = {(cuuint32_t)kBoxCols, (cuuint32_t)kblocks, 1};
+  cuuint32_t box[3] = {(cuuint32_t)kBoxCols, (cuuint32_t)kblocks, (cuuint32_t)box_rows};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, dtype == VLR_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                   3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1278,11 +1301,16 @@ static int make_map_row3(CUtensorMap* map, const void* ptr, int dtype, int64_t r
 }
 
 int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, int64_t w_rows,
-                 int64_t cols, int dtype) {
+                 int64_t cols, int dtype, bool gather_weight_maps) {
   int rc;
   if (cols % kBoxCols == 0 && cols / kBoxCols >= 8)
-    for (int i = 0; i < 3; ++i)
+    for (int i = 0; i < 3; ++i) {
       if ((rc = make_map_row3(&set->row3[i], act, dtype, act_rows, cols, 2 << i)) != VLR_OK) return rc;
+      for (int b = 0; b < 4 && gather_weight_maps; ++b)
+        if ((16 << b) * (2 << i) <= 256 &&
+            (rc = make_map_row3(&set->w3[i][b], w, dtype, w_rows, cols, 2 << i, 16 << b)) != VLR_OK)
+          return rc;
+    }
   for (int i = 0; i < 3; ++i)
     if ((rc = make_map_2d(&set->act[i], act, dtype, act_rows, cols, 32 << i)) != VLR_OK) return rc;
   for (int i = 0; i < 4; ++i)

@@ -20,6 +20,9 @@ struct alignas(128) MapSet {
   CUtensorMap row3[3];  // one activation row x 2 / 4 / 8 consecutive 64-column blocks, as a 3-D view
                         // [rows][cols / 64][64] of the activations (cols a multiple of 64, else unset):
                         // the blocks land as consecutive 128-byte lines
+  CUtensorMap w3[3][4]; // [i][b]: 16 << b pool cells x (2 << i) consecutive 64-column blocks of the same 3-D view
+                        // of the pool (set where cells x blocks <= 256, in step plans' shrink side only):
+                        // a cell's blocks land as consecutive lines, cell after cell
 };
 
 struct alignas(128) StepProblem {
@@ -122,7 +125,7 @@ int sm_count();
 // launchers shared between the single-problem entry points and the step entry point
 int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int box_rows);
 int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, int64_t w_rows,
-                 int64_t cols, int dtype);
+                 int64_t cols, int dtype, bool gather_weight_maps = false);
 int bgmv_gather_launch(void* y, const void* x, const void* w, const void* scales,
                        const BgmvGroups& groups, int64_t max_groups, int h_in, int h_out,
                        int layout, int dtype, cudaStream_t stream, int n_problems);
