@@ -334,13 +334,11 @@ size_t vlr_lora_step_workspace_bytes(int64_t T, int n_problems);
 #define VLR_STEP_WIDE_GATHER_STAGES 32
 #define VLR_STEP_ALL_WIDE_GATHER_STAGES 64
 /* or-ed into phase_mask.  With max_rank above 64: each tensor-core kernel is launched twice,
- * once over the tiles of adapters of rank <= 64 and once over the others, so that the first
- * launch cuts its 192 KB operand ring for those ranks (four stages) instead of for the
- * largest rank of the step (three): in a batch of mixed ranks the tiles up to rank 64 ran
- * 18-34 % slower on the three-stage ring.  A small kernel ahead of them lists each class's
+ * once over the consecutive-row tiles of adapters above rank 64, which need the 192 KB operand
+ * ring cut into three stages, and once over all other tiles (consecutive rows up to rank 64,
+ * gather tiles of any rank), which fit four stages and ran 18-34 % slower on three.  A small kernel ahead of them lists each class's
  * tiles in the workspace; the second class runs on a library-owned side stream, forked from
- * and joined to `stream` inside the call.  Set it when adapters of both classes are
- * resident; same results bit for bit. */
+ * and joined to `stream` inside the call.  Same results bit for bit. */
 #define VLR_STEP_SPLIT_RANK_CLASSES 128
 int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, const int32_t* tiles,
                   const int32_t* gather_rows, int64_t max_mma_tiles, int64_t max_gather_tiles,

@@ -1079,10 +1079,10 @@ def test_results_do_not_depend_on_the_tile_table(ops):
 
 
 def test_rank_class_split_changes_nothing(ops):
-    """With adapters on both sides of rank 64 resident a step launches each tensor-core kernel
-    once per rank class (VLR_STEP_SPLIT_RANK_CLASSES).  Every tile is taken by exactly one of
-    the two launches: the results equal those of the single launch bit for bit, and a rank the
-    kernels do not support is still reported."""
+    """With an adapter above rank 64 resident a step launches each tensor-core kernel twice
+    (VLR_STEP_SPLIT_RANK_CLASSES): once over the consecutive-row tiles above rank 64, once over
+    all other tiles.  Every tile is taken by exactly one of the two launches: the results equal
+    those of the single launch bit for bit."""
     from valora_b200.engine import LoraStepEngine
     dtype = torch.bfloat16
     b4 = workloads.config4(n_gpus=8, rank=5)
@@ -1094,7 +1094,8 @@ def test_rank_class_split_changes_nothing(ops):
     assert unused
     lone = np.minimum(b4.ranks, 64)
     lone[unused[0]] = 128
-    for ranks in (b4.ranks, lone):
+    # third case: every adapter at rank 128 - gather tiles on the four-stage ring, consecutive rows on three
+    for ranks in (b4.ranks, lone, np.full_like(b4.ranks, 128)):
         scal = (workloads.ALPHA / ranks).astype(np.float32)
         outs = []
         for split in (True, False):

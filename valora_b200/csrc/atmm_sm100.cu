@@ -1364,10 +1364,11 @@ static const vlr_tile_choice_t* find_choice(int step, int max_rank) {
   return best;
 }
 
-static void size_rings(TileSource& src, int max_rank, bool step) {
+static void size_rings(TileSource& src, int max_rank, bool step, int ring_rank = 0) {
   if (max_rank <= 0 || max_rank > kMaxRank) max_rank = kMaxRank;
-  const int pad = (max_rank + 15) & ~15;
   src.max_rank = max_rank;
+  if (ring_rank > 0 && ring_rank < max_rank) max_rank = ring_rank;      // what the ring is cut for
+  const int pad = (max_rank + 15) & ~15;
   const vlr_tile_choice_t* c = find_choice(step ? 1 : 0, max_rank);
   // without an entry: 48 KB stages while a full tile's two K blocks fit, else 64 KB
   src.shrink_stages = c ? c->shrink_stages : (pad <= 64 ? 4 : 3);
@@ -1432,7 +1433,7 @@ static int launch_atmm(void* y, const void* x, const void* w, const void* scales
 #endif
   const bool step = src.plan != nullptr;
   // rank bound: the caller's hint in a step, the width of the rank-side buffer otherwise
-  size_rings(src, step ? src.max_rank : (h_in >= h_out ? h_out : h_in), step);
+  size_rings(src, step ? src.max_rank : (h_in >= h_out ? h_out : h_in), step, step ? src.ring_rank : 0);
   int rc;
   if (h_in >= h_out) {
     if (!step && (rc = make_map_set(&maps, x, T_rows, w, w_cells, h_in, dtype)) != VLR_OK) return rc;

@@ -114,8 +114,11 @@ struct TileSource {
   int tile_rows;                     // mode 0, shrink: rows per tile (32 or 128; 0 = 128)
   int n_problems;
   int nsplit;                        // expand: work items per tile (column shares)
-  // operand rings, sized by the launcher from the largest rank the launch may meet
+  // operand rings, sized by the launcher from the largest rank the launch may meet - or, where
+  // set, from ring_rank: the largest rank among the tiles whose stages need the ring cut for
+  // them (consecutive-row tiles; the stages of a gather tile fit a 48 KB stage at every rank)
   int max_rank;
+  int ring_rank;
   int shrink_stages, shrink_stage_bytes;
   int exp_stages, exp_stage_bytes;
 };

@@ -37,8 +37,9 @@ SideStream* side_stream() {
   return &slots[dev];
 }
 
-// The step's tiles by rank class: indices of the tiles of rank <= split_rank in list1, of the others
-// in list2, each in the order of `tiles`; the two counts in cls_count[0], cls_count[16] (64 bytes
+// The step's tiles in two classes: list2 gets the indices of the consecutive-row tiles of rank >
+// split_rank, list1 those of every other tile (consecutive rows up to that rank, and gather tiles
+// of any rank: their stages fit the deeper ring's 48 KB at every rank), each in the order of `tiles`; the two counts in cls_count[0], cls_count[16] (64 bytes
 // apart).  One CTA; n is a few thousand at most.
 __global__ void __launch_bounds__(1024)
 classify_tiles_kernel(const int32_t* __restrict__ tiles, const int32_t* __restrict__ counts, int gather_mma,
@@ -53,7 +54,8 @@ classify_tiles_kernel(const int32_t* __restrict__ tiles, const int32_t* __restri
   for (int b0 = 0; b0 < n; b0 += 1024) {
     const int b = b0 + tid;
     const bool in = b < n;
-    const bool c2 = in && tiles[(int64_t)b * VLR_TILE_INTS + 2] > split_rank;
+    const bool c2 = in && tiles[(int64_t)b * VLR_TILE_INTS] == VLR_TILE_MMA &&
+                    tiles[(int64_t)b * VLR_TILE_INTS + 2] > split_rank;
     const bool c1 = in && !c2;
     const unsigned m1 = __ballot_sync(0xffffffffu, c1), m2 = __ballot_sync(0xffffffffu, c2);
     if (lane == 0) { w1[warp] = __popc(m1); w2[warp] = __popc(m2); }
@@ -178,10 +180,11 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
   // projection is narrower than the rank buffer must still go the right way.
   const int shrink_h_in = (int)max_h_in > kMaxRank ? (int)max_h_in : kMaxRank;
   const int expand_h_out = (int)max_h_out > kMaxRank ? (int)max_h_out : kMaxRank + 8;
-  // With adapters on both sides of rank 64, a kernel runs once per rank class: the launch for
-  // ranks <= 64 then has the four-stage ring those tiles are fastest on.  The classes share no
-  // adapter, so shrink and expand of one class depend on nothing of the other: the second
-  // class runs on a side stream, its CTAs moving onto the SMs as the first class's kernels
+  // With adapters above rank 64 resident, a kernel runs once per class of tiles: consecutive-row
+  // tiles above rank 64 need the three-stage ring (64 KB stages); every other tile - consecutive
+  // rows up to rank 64, gather tiles of any rank - runs on the four-stage ring, on which they are
+  // 18-34 % faster.  A row belongs to one tile, so shrink and expand of one class read and write
+  // nothing of the other: the second class runs on a side stream, its CTAs moving onto the SMs as the first class's kernels
   // run out of tiles (one tail per step instead of one per launch - with two tails config 2's
   // large prefill tiles lost more than the deeper ring gained).
   const bool split = (phase_mask & VLR_STEP_SPLIT_RANK_CLASSES) && src.max_rank > 64 &&
@@ -191,11 +194,11 @@ extern "C" int vlr_lora_step(const void* plan_dev, int n_problems, int64_t T, co
     const int flags = expand ? VLR_ATMM_APPLY_SCALE : 0;
     TileSource a = src;
     a.item_counter = counters + (expand ? 32 : 0) + (cls == 2 ? 16 : 0);
-    if (cls == 1) {                                    // ranks <= 64
-      a.max_rank = 64;
+    if (cls == 1) {                                    // consecutive rows up to rank 64, gather tiles of any rank
+      a.ring_rank = 64;
       a.class_list = cls_list1;
       a.class_count = cls_count;
-    } else if (cls == 2) {                             // ranks above 64
+    } else if (cls == 2) {                             // consecutive rows above rank 64
       a.class_list = cls_list2;
       a.class_count = cls_count + 16;
       a.wide_below_rank = 0;                           // wide stages are for small ranks

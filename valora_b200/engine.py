@@ -180,9 +180,10 @@ class LoraStepEngine:
             wide = ops.STEP_WIDE_GATHER_STAGES if min(self.ranks) < self._wide_below else 0
         else:
             wide = (ops.STEP_WIDE_GATHER_STAGES | ops.STEP_ALL_WIDE_GATHER_STAGES) if self.wide_gather else 0
-        # adapters on both sides of rank 64 resident: one launch per rank class, each with the
-        # operand ring cut for its ranks (split_rank_classes=False keeps one launch per kernel)
-        split = ops.STEP_SPLIT_RANK_CLASSES if (self.split_rank_classes and min(self.ranks) <= 64 < max(self.ranks)) else 0
+        # an adapter above rank 64 resident: its consecutive-row tiles need the three-stage ring; they get
+        # a launch of their own, and every other tile the four-stage ring (split_rank_classes=False
+        # keeps one launch per kernel)
+        split = ops.STEP_SPLIT_RANK_CLASSES if (self.split_rank_classes and max(self.ranks) > 64) else 0
         return ops.STEP_GATHER_ON_TENSOR_CORES | wide | split
 
     def phases(self):
