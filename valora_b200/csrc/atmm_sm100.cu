@@ -890,6 +890,13 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
       const bool mine = ti.gather && lane < ti.rows;
       const T* yrow = mine ? yg + (int64_t)grow_l * er.h_out : yg;
       if (lane < 7) prefetch_tensormap(lane < 3 ? &ms->act[lane] : &ms->w[lane - 3]);
+      // tiles of a step whose rank rows are one box (16 / 32 / 64 / 128): the stage's column
+      // blocks come as ONE copy of eight, four or two blocks - the same bytes to the same places as one
+      // box per block, but the pieces of a weight row are then requested close together
+      const int wb = (k_pad == 16) ? 0 : (k_pad == 32) ? 1 : (k_pad == 64) ? 2 : (k_pad == 128) ? 3 : -1;
+      const bool blocks3 = src.plan != nullptr && wb >= 0 && (er.h_out & (kBoxCols - 1)) == 0;
+      if (blocks3 && lane >= 8 && lane < (wb < 2 ? 11 : 10)) prefetch_tensormap(&ms->wb3[wb][lane - 8]);
+      if (src.plan != nullptr && lane == 11) prefetch_tensormap(&ms->act3);
       for (int t = 0; t < er.nt_count; ++t, ++it) {
         if ((int)(it % kExpProducers) != pw) continue;            // the other producer's stage
         const int s = it % nst;
@@ -904,13 +911,31 @@ atmm_expand_kernel(const __grid_constant__ MapSet maps_,
               bytes = (uint32_t)ncb * (uint32_t)k_pad * 128u +
                       (uint32_t)y_rows * (uint32_t)min(er.tile_n, er.h_out - n0) * 2u;
             mbar_expect_tx(full_bar(s), bytes);
-            for (int cb = 0; cb < ncb; ++cb)
+            int cb = 0;
+            if (blocks3) {
+              if (wb < 2)
+                for (; ncb - cb >= 8; cb += 8)
+                  tma_load_3d(b_stage(s) + cb * er.bstride, &ms->wb3[wb][2], 0, (int)ti.wrow0, n0 / kBoxCols + cb,
+                              full_bar(s));
+              for (; ncb - cb >= 4; cb += 4)
+                tma_load_3d(b_stage(s) + cb * er.bstride, &ms->wb3[wb][1], 0, (int)ti.wrow0, n0 / kBoxCols + cb,
+                            full_bar(s));
+              for (; ncb - cb >= 2; cb += 2)
+                tma_load_3d(b_stage(s) + cb * er.bstride, &ms->wb3[wb][0], 0, (int)ti.wrow0, n0 / kBoxCols + cb,
+                            full_bar(s));
+            }
+            for (; cb < ncb; ++cb)
               load_w_rows(b_stage(s) + cb * er.bstride, ms, n0 + cb * kBoxCols, (int)ti.wrow0,
                           k_pad, full_bar(s));
-            if (!ti.gather)
-              for (int cb = 0; cb < ncb; ++cb)
-                load_act_rows((b_stage(s) + er.yoff) + cb * (kTileM * 128), ms, n0 + cb * kBoxCols, ti.row0,
-                              ti.rows, full_bar(s));
+            if (!ti.gather) {
+              // a full tile's two Y blocks as one copy where the plan has the map for it
+              if (src.plan != nullptr && y_rows == kTileM && ncb == 2 && (er.h_out & (kBoxCols - 1)) == 0)
+                tma_load_3d(b_stage(s) + er.yoff, &ms->act3, 0, ti.row0, n0 / kBoxCols, full_bar(s));
+              else
+                for (int cb2 = 0; cb2 < ncb; ++cb2)
+                  load_act_rows((b_stage(s) + er.yoff) + cb2 * (kTileM * 128), ms, n0 + cb2 * kBoxCols, ti.row0,
+                                ti.rows, full_bar(s));
+            }
           }
         }
         if (lane == 0 && !ok && !ti.gather) break;
@@ -1300,13 +1325,38 @@ static int make_map_row3(CUtensorMap* map, const void* ptr, int dtype, int64_t r
   return r == CUDA_SUCCESS ? VLR_OK : VLR_ERR_DRIVER;
 }
 
+// [cols / 64][rows][64] view of a row-major [rows, cols] tensor: box = nblocks 64-column blocks x box_rows rows
+static int make_map_blocks3(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int nblocks,
+                            int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return VLR_ERR_DRIVER;
+  cuuint64_t dims[3] = {(cuuint64_t)kBoxCols, (cuuint64_t)rows, (cuuint64_t)(cols / kBoxCols)};
+  cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)kBoxCols * 2};
+  cuuint32_t box[3] = {(cuuint32_t)kBoxCols, (cuuint32_t)box_rows, (cuuint32_t)nblocks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dtype == VLR_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                  3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? VLR_OK : VLR_ERR_DRIVER;
+}
+
 int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, int64_t w_rows,
-                 int64_t cols, int dtype, bool gather_weight_maps) {
+                 int64_t cols, int dtype, int gather_weight_maps) {
   int rc;
+  if (gather_weight_maps == 2 && cols % kBoxCols == 0 &&
+      (rc = make_map_blocks3(&set->act3, act, dtype, act_rows, cols, 2, kTileM)) != VLR_OK)
+    return rc;
+  if (gather_weight_maps == 2 && cols % kBoxCols == 0)
+    for (int b = 0; b < 4; ++b)
+      for (int i = 0; i < 3; ++i)
+        if ((i < 2 || b < 2) &&
+            (rc = make_map_blocks3(&set->wb3[b][i], w, dtype, w_rows, cols, 2 << i, 16 << b)) != VLR_OK)
+          return rc;
   if (cols % kBoxCols == 0 && cols / kBoxCols >= 8)
     for (int i = 0; i < 3; ++i) {
       if ((rc = make_map_row3(&set->row3[i], act, dtype, act_rows, cols, 2 << i)) != VLR_OK) return rc;
-      for (int b = 0; b < 4 && gather_weight_maps; ++b)
+      for (int b = 0; b < 4 && gather_weight_maps == 1; ++b)
         if ((16 << b) * (2 << i) <= 256 &&
             (rc = make_map_row3(&set->w3[i][b], w, dtype, w_rows, cols, 2 << i, 16 << b)) != VLR_OK)
           return rc;

@@ -23,6 +23,11 @@ struct alignas(128) MapSet {
   CUtensorMap w3[3][4]; // [i][b]: 16 << b pool cells x (2 << i) consecutive 64-column blocks of the same 3-D view
                         // of the pool (set where cells x blocks <= 256, in step plans' shrink side only):
                         // a cell's blocks land as consecutive lines, cell after cell
+  CUtensorMap wb3[4][3];// [b][i]: 16 << b pool cells x (2 << i) 64-column blocks (8 blocks: 16 / 32 cells only) with the block as the OUTER
+                        // dimension (view [cols / 64][cells][64]): the blocks land one after the other, each
+                        // [cells][64] - what one box per block gives, requested as one copy (step plans'
+                        // expand side only)
+  CUtensorMap act3;     // 128 activation rows x two 64-column blocks, block-major like wb3 (same side)
 };
 
 struct alignas(128) StepProblem {
@@ -128,7 +133,7 @@ int sm_count();
 // launchers shared between the single-problem entry points and the step entry point
 int make_map_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int box_rows);
 int make_map_set(MapSet* set, const void* act, int64_t act_rows, const void* w, int64_t w_rows,
-                 int64_t cols, int dtype, bool gather_weight_maps = false);
+                 int64_t cols, int dtype, int gather_weight_maps = 0);   // 1: w3 (shrink side), 2: wb3 (expand side)
 int bgmv_gather_launch(void* y, const void* x, const void* w, const void* scales,
                        const BgmvGroups& groups, int64_t max_groups, int h_in, int h_out,
                        int layout, int dtype, cudaStream_t stream, int n_problems);

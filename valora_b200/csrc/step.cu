@@ -101,8 +101,8 @@ extern "C" int vlr_step_plan_build(const vlr_problem_t* problems, int n_problems
     StepProblem sp;
     memset(&sp, 0, sizeof(sp));
     int rc;
-    if ((rc = make_map_set(&sp.shrink, p.x, max_rows, p.wa, p.cells_a, p.h_in, dtype, true)) != VLR_OK) return rc;
-    if ((rc = make_map_set(&sp.expand, p.y, max_rows, p.wb, p.cells_b, p.h_out, dtype)) != VLR_OK) return rc;
+    if ((rc = make_map_set(&sp.shrink, p.x, max_rows, p.wa, p.cells_a, p.h_in, dtype, 1)) != VLR_OK) return rc;
+    if ((rc = make_map_set(&sp.expand, p.y, max_rows, p.wb, p.cells_b, p.h_out, dtype, 2)) != VLR_OK) return rc;
     sp.x = p.x; sp.y = p.y; sp.wa = p.wa; sp.wb = p.wb;
     sp.a_start_a = p.a_start_a; sp.a_loc_a = p.a_loc_a;
     sp.a_start_b = p.a_start_b; sp.a_loc_b = p.a_loc_b;
