@@ -1,6 +1,6 @@
 // One step over many LoRA projections: the step plan (per-problem tensor maps
-// and pointers in device memory) and the four batched launches that run the
-// shrink and the expand of every problem of a packed batch.
+// and pointers in device memory) and the batched launches that run the shrink
+// and the expand of every problem of a packed batch.
 #include <string.h>
 
 #include <mutex>
@@ -39,8 +39,9 @@ SideStream* side_stream() {
 
 // The step's tiles in two classes: list2 gets the indices of the consecutive-row tiles of rank >
 // split_rank, list1 those of every other tile (consecutive rows up to that rank, and gather tiles
-// of any rank: their stages fit the deeper ring's 48 KB at every rank), each in the order of `tiles`; the two counts in cls_count[0], cls_count[16] (64 bytes
-// apart).  One CTA; n is a few thousand at most.
+// of any rank: their stages fit the deeper ring's 48 KB at every rank), each in the order of
+// `tiles`; the two counts in cls_count[0] and cls_count[16] (64 bytes apart).  One CTA; n is a
+// few thousand at most.
 __global__ void __launch_bounds__(1024)
 classify_tiles_kernel(const int32_t* __restrict__ tiles, const int32_t* __restrict__ counts, int gather_mma,
                       int split_rank, int cap, int32_t* cls_count, int32_t* list1, int32_t* list2) {
