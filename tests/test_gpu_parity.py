@@ -790,15 +790,21 @@ def test_step_shared_inputs_match_private_copies(ops):
         LoraStepEngine([("a", 512, 512), ("b", 256, 512)], b.ranks, b.scalings(), b.dtype, DEV, 1, b.T, input_of=[0, 0])
 
 
-def test_step_replays_from_a_cuda_graph(ops):
+@pytest.mark.parametrize("mixed_ranks", [False, True])
+def test_step_replays_from_a_cuda_graph(ops, mixed_ranks):
     """packer + shrink + expand captured once, replayed on batches whose token -> adapter
     map changes between replays: the schedule is rebuilt on the device inside the graph,
-    so every replay must equal an eager step on the same inputs, bit for bit."""
+    so every replay must equal an eager step on the same inputs, bit for bit.  With ranks
+    above 64 in the pool the step forks a side stream for one class of tiles and joins it
+    again: that too has to sit inside the captured graph."""
     from valora_b200.engine import LoraStepEngine
     b = workloads.config3(layers=1)
+    if mixed_ranks:
+        b.ranks = np.random.default_rng(6).choice(np.array([16, 64, 128]), size=b.n_adapters).astype(np.int64)
     projs = [("q", 1024, 1024), ("up", 1024, 2048)]
     L = 2
     eng = LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, L, b.T)
+    assert bool(eng._gather_flag() & ops.STEP_SPLIT_RANK_CLASSES) == mixed_ranks
     eng.randomize_weights(seed=12)
     g = torch.Generator(device=DEV)
     g.manual_seed(13)
