@@ -708,9 +708,13 @@ def test_step_from_host_buffers_matches_resident_step(ops, overlap):
     a row (the second call re-uses the device buffers the first one wrote)."""
     from valora_b200.engine import LoraStepEngine
     b = workloads.config0()
+    if overlap:
+        # ranks on both sides of 64: every layer's call forks and joins the side stream of the tile classes
+        b.ranks = np.array([8, 128, 16, 72], np.int64)
     projs = [("q", 512, 512), ("up", 512, 1024)]
     L = 3
     eng = LoraStepEngine(projs, b.ranks, b.scalings(), b.dtype, DEV, L, b.T)
+    assert bool(eng._gather_flag() & ops.STEP_SPLIT_RANK_CLASSES) == bool(overlap)
     eng.randomize_weights(seed=5)
     g = torch.Generator().manual_seed(9)
     xh = [[torch.randn(b.T, hi, generator=g).to(b.dtype).pin_memory() for _, hi, _ in projs] for _ in range(L)]
